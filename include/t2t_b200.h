@@ -1,0 +1,142 @@
+/* C ABI of libt2t_b200.so: the Token2Tile sparse attention operator for B200
+ * (sm_100a).
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream, does
+ * no allocation and no host synchronisation, and returns T2T_OK or an error
+ * code after checking cudaGetLastError().  Workspaces are owned by the caller;
+ * the *_ws_bytes functions give their sizes.  `d_status` (may be NULL) is a
+ * device int that a kernel sets to a non-zero T2T_ST_* value when one of its
+ * bounded waits gave up.
+ *
+ * Shapes use H heads, N tokens, D = 128, r = 32, C = 2048 key clusters and CQ
+ * query clusters.  "bf16" tensors are row-major and contiguous.  Each function
+ * names the reference interface it replaces by path:line inside the reference
+ * project (token2tile/operator/...).
+ */
+#ifndef T2T_B200_H_
+#define T2T_B200_H_
+
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  T2T_OK = 0,
+  T2T_ERR_ARG = 1,        /* null pointer, non-positive size, unsupported shape */
+  T2T_ERR_CUDA = 2,       /* a launch or attribute call failed */
+  T2T_ERR_WORKSPACE = 3,  /* workspace too small */
+};
+enum {
+  T2T_ST_OK = 0,
+  T2T_ST_WAIT_TIMEOUT = 1,
+  T2T_ST_BAD_PLAN = 2,
+};
+
+/* Library version as major * 10000 + minor * 100 + patch. */
+int t2t_version(void);
+
+/* out[h,n,:] = bf16(x[h,n,:] . U[h]) with fp32 accumulation on the tensor
+ * cores.  x bf16 [H,N,128], U bf16 [H,128,32], out bf16 [H,N,32].
+ * Replaces torch.bmm(q, Uq, out=QU) / torch.bmm(k, Uk, out=KU),
+ * deploy_step.py:321-324 and :252-253. */
+int t2t_project(const void* x, const void* U, void* out, int H, int N, int* d_status,
+                cudaStream_t stream);
+
+/* labels[h,i] = argmin_c(||c||^2 - 2 x_i.c), ties to the lowest c; rows >=
+ * pin_begin get pin_label when pin_begin >= 0.  x bf16 [H,N,32], cen bf16
+ * [H,Cn,32], labels int32 [H,N].  The distance is the fp32 fused-multiply-add
+ * chain over k = 0..31 started at ||c||^2, so labels are reproducible bit for
+ * bit on any machine.  Replaces fast_assign(x, centroids), fast_assign.py:79-106
+ * and assign_kernel, kernels/kmeans_maintain/src/kernels.cu:104-257. */
+int t2t_assign(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
+               int pin_label, cudaStream_t stream);
+
+/* Deterministic centroid update from labels: integer fixed-point (2^15) sums,
+ * newc = bf16(float(sum) / (2^15 n)), an empty cluster keeps `old`.  x bf16
+ * [H,N,32], labels int32 [H,N], old/newc bf16 [H,Cn,32], counts int32 [H,Cn].
+ * Replaces fused_update_vstats(ku, labels, old, None),
+ * fused_update_vstats.py:72-115 (its deterministic form,
+ * integrations/sglang/backend/t2t_attn.py:242-257). */
+size_t t2t_centroid_update_ws_bytes(int H, int N, int Cn);
+int t2t_centroid_update(const void* x, const void* labels, const void* old, void* newc, void* counts,
+                        int H, int N, int Cn, void* ws, size_t ws_bytes, cudaStream_t stream);
+
+/* One structure rebuild: two Lloyd passes for the queries (from cq0), one for
+ * the keys (from ck0), stable grouping of both, fp32 key means, cluster-major
+ * V and the per-cluster value sums.  Outputs: qlab/klab int32 [H,N], cq2 bf16
+ * [H,CQ,32], ck2 fp32 [H,C,32], ck16 = bf16(ck2), cks16 = bf16(ck2 * scale),
+ * qcounts int32 [H,CQ], qperm/kperm int32 [H,N] (sorted position -> row),
+ * kcounts int32 [H,C], V_sorted bf16 [H,N,128], sumv bf16 [H,C,128] (value sums
+ * divided by lam), lam fp32 [H].  The last pin_tail keys are forced into
+ * cluster C-1.  Replaces kmeans_maintain_launch,
+ * kernels/kmeans_maintain/src/kernels.h:5-13 (kernels.cu:787-876) and the casts
+ * at deploy_step.py:389-393. */
+size_t t2t_kmeans_maintain_ws_bytes(int H, int N, int CQ, int C);
+int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const void* cq0, const void* ck0,
+                        void* qlab, void* cq2, void* klab, void* ck2, void* ck16, void* cks16,
+                        void* qcounts, void* qperm, void* kcounts, void* kperm, void* V_sorted,
+                        void* sumv, void* lam, float scale, int H, int N, int CQ, int C, int pin_tail,
+                        void* ws, size_t ws_bytes, cudaStream_t stream);
+
+/* Reuse call: V_sorted = V[kperm], value sums and lam from this call's V with
+ * the stored grouping.  Replaces reuse_vstats_gather_launch,
+ * kernels/kmeans_maintain/src/kernels.h:22-26 (kernels.cu:900-923). */
+size_t t2t_vstats_gather_ws_bytes(int H, int C);
+int t2t_vstats_gather(const void* V, const void* kperm, const void* kcounts, void* V_sorted, void* sumv,
+                      void* lam, int H, int N, int C, void* ws, size_t ws_bytes, cudaStream_t stream);
+
+/* out[h,i,:] = x[h,perm[h,i],:] for rows of 128 bf16.  Replaces
+ * fast_gather(x, perm, out), fast_permute.py:54-56. */
+int t2t_gather_rows(const void* x, const void* perm, void* out, int H, int N, cudaStream_t stream);
+
+/* Scoring and selection fused: g = fp16(QU_i . cks_c) (fp32 chain), clusters
+ * ordered by (g descending, index ascending), a cluster is selected iff the
+ * sizes before it sum to < *ns; the selections of a query cluster are OR-ed
+ * into unip int32 [H,CQ,64] (bit b of word w = cluster 32 w + b); rowcnt int32
+ * [H,N] is the selected token count per query.  qperm/tile_sizes are the query
+ * grouping; ns is a device int32 read by the kernel; pin_tail > 0 also sets
+ * cluster C-1 in every row.  The [H,N,2048] score matrix is never stored.
+ * Replaces torch.bmm(QU, cks^T, out=gl), deploy_step.py:394, and
+ * fscu_packed_launch / fscu_split_packed_launch,
+ * kernels/select_union/src/kernel.h:19-29 (kernel.cu:523-556), and the
+ * pin_tail OR at deploy_step.py:444-448. */
+int t2t_score_select_union(const void* QU, const void* cks, const void* kcounts, const void* qperm,
+                           const void* tile_sizes, const int* ns, void* unip, void* rowcnt, int H,
+                           int N, int CQ, int pin_tail, cudaStream_t stream);
+
+/* Task plan + exact attention over the unions + centroid residual + merge.
+ * q bf16 [H,N,128] original order; kp/vp bf16 [H,N,128] cluster-major;
+ * tile_sizes int32 [H,CQ]; kcounts int32 [H,C]; unip int32 [H,CQ,64]; QU bf16
+ * [H,N,32]; cks bf16 [H,C,32]; sumv bf16 [H,C,128]; lam fp32 [H]; qlab, qperm
+ * int32 [H,N]; tailw device fp32; out bf16 [H,N,128] original order.  plan
+ * (t2t_tile_attn_plan_ints ints) belongs to the structure snapshot and is
+ * rebuilt when rebuild_plan != 0; ws (t2t_tile_attn_ws_bytes) holds the
+ * intermediate exact output and log-sum-exp.  Replaces launch_cluster_attn +
+ * launch_tail_merge, kernels/tile_attn/src/main.cpp:5-14, 24-50 and
+ * plan_workspace_ints, main.cpp:16-22. */
+size_t t2t_tile_attn_plan_ints(int H, int N, int CQ);
+size_t t2t_tile_attn_ws_bytes(int H, int N);
+int t2t_tile_attn(const void* q, const void* kp, const void* vp, const void* tile_sizes,
+                  const void* kcounts, const void* unip, const void* QU, const void* cks,
+                  const void* sumv, const void* lam, const void* qlab, const void* qperm,
+                  const float* tailw, void* out, int* plan, int rebuild_plan, int H, int N, int CQ,
+                  void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
+
+/* Number of tasks and executed (query, key) pairs of the current plan, for
+ * FLOP accounting: info[0] = tasks, info[1..2] = pairs as low/high 32 bits.
+ * Device-side; copies 4 ints into d_info. */
+int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, int* d_info, cudaStream_t stream);
+
+/* Tensor-core self-test: S = A . B^T, O = bf16(S / 16) . V for 128 x 128 bf16
+ * operands, through the same shared-memory / TMEM operand forms the attention
+ * kernels use.  No counterpart in the reference. */
+int t2t_umma_selftest(const void* A, const void* B, const void* V, float* S_out, float* O_out,
+                      int* d_status, cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* T2T_B200_H_ */

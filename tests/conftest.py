@@ -1,0 +1,41 @@
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+@pytest.fixture(scope="session")
+def lib():
+    from token2tile_b200 import _lib
+    return _lib.load()
+
+
+@pytest.fixture(scope="session")
+def small_case():
+    """H=2, N=4096 locality-mixture inputs and an oracle state (CPU tensors)."""
+    from oracle import t2t_oracle as O
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    H, N, CQ = 2, 4096, 32
+    q, k, v = locality_mixture(H, GRIDS["cpu"])
+    op = O.OracleOperator(H, N, CQ, s_frac=0.05)
+    state = op.init_state(q, k)
+    return dict(H=H, N=N, CQ=CQ, q=q, k=k, v=v, state=state)

@@ -1,0 +1,796 @@
+// Task plan, packed exact tile attention and centroid residual + merge.
+//
+// Replaces the reference's tile_attn extension
+// (token2tile/operator/kernels/tile_attn/src/kernel.cu: selected_kv_lengths,
+// plan_kernel, attn_kernel, tail_wgmma_kernel), whose wgmma kernels do not
+// exist on sm_100a.  Both hot kernels run their matrix products on the
+// tcgen05 tensor cores with fp32 accumulators in tensor memory (TMEM):
+//
+//   attention:  S = Q K^T   (128 queries x 128 keys, K = 128)   operands in smem
+//               O += P V    (P = exp2(S - m) as bf16 in TMEM, V in smem)
+//   residual :  S = QU cks^T (128 queries x 128 centroids, K = 32)
+//               T += P sumv (128 x 128, K = 128 centroids)
+//
+// One thread owns one query row (TMEM lane), so row maxima and sums need no
+// shuffles.  K/V rows of a union are contiguous runs in the cluster-major
+// copies kp/vp and are gathered with 16-byte cp.async into 128-byte-swizzled
+// tiles.  Two CTAs share an SM (256 TMEM columns each) so that the softmax of
+// one overlaps the MMAs and loads of the other.  Every mbarrier wait is
+// bounded; on a timeout the CTA raises a status word and leaves.
+#include "common.cuh"
+#include "t2t_b200.h"
+
+namespace t2t {
+
+constexpr int QT = 128;          // query rows per task
+constexpr int KT = 128;          // keys per tile
+constexpr int MAX_RUNS = 1024;   // runs of selected clusters in one union
+constexpr int PLAN_SORT_MAX = 2048;
+constexpr int PLAN_HDR = 8;      // counters: [0] tasks, [1] attention cursor, [2..3] executed pairs (lo, hi)
+
+__host__ __device__ inline size_t plan_task_offset(int H) { return ((size_t)H * (kC + 1) + PLAN_HDR + 3) & ~(size_t)3; }
+__host__ __device__ inline size_t plan_max_tasks(int H, int N, int CQ) { return (size_t)H * (CQ + cdiv(N, QT) + 1); }
+
+struct PlanView {
+  int* k_off;      // [H][C + 1]
+  int* counters;   // [PLAN_HDR]
+  int4* tasks;     // (head, query cluster, first sorted row, rows)
+  int* kv_lens;    // [H][CQ]
+};
+__host__ __device__ inline PlanView plan_view(int* plan, int H, int N, int CQ) {
+  PlanView v;
+  v.k_off = plan;
+  v.counters = plan + (size_t)H * (kC + 1);
+  v.tasks = reinterpret_cast<int4*>(plan + plan_task_offset(H));
+  v.kv_lens = plan + plan_task_offset(H) + 4 * plan_max_tasks(H, N, CQ);
+  return v;
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------
+// plan
+// ---------------------------------------------------------------------------
+// tokens in the union of every query cluster (0 for an empty query cluster)
+__global__ void __launch_bounds__(256) kvlen_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz,
+                                                    const uint32_t* __restrict__ ub, int* __restrict__ kv_lens,
+                                                    int CQ) {
+  const int h = blockIdx.y, c = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (c >= CQ) return;
+  int total = 0;
+  if (qsz[(size_t)h * CQ + c] > 0) {
+    const uint32_t* words = ub + ((size_t)h * CQ + c) * (kC / 32);
+    for (int w = lane; w < kC / 32; w += 32) {
+      uint32_t bits = words[w];
+      while (bits) {
+        const int b = __ffs(bits) - 1;
+        total += ksz[(size_t)h * kC + w * 32 + b];
+        bits &= bits - 1;
+      }
+    }
+  }
+  total = __reduce_add_sync(0xffffffffu, total);
+  if (lane == 0) kv_lens[(size_t)h * CQ + c] = total;
+}
+
+__device__ __forceinline__ int block_excl_scan_256(int v, int* ws, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int inc = warp_incl_scan(v, lane);
+  __syncthreads();
+  if (lane == 31) ws[warp] = inc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < 8; ++i) { const int t = ws[i]; ws[i] = acc; acc += t; }
+    ws[8] = acc;
+  }
+  __syncthreads();
+  total = ws[8];
+  return inc - v + ws[warp];
+}
+
+// One CTA per head: key-cluster offsets, tasks of at most QT rows (a query
+// cluster is split evenly), longest-processing-time order inside the head.
+__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz, int H,
+                                                   int N, int CQ, int* __restrict__ plan) {
+  __shared__ int ws[16];
+  __shared__ unsigned long long skey[PLAN_SORT_MAX];
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  const int h = blockIdx.x, tid = threadIdx.x;
+
+  int running = 0;
+  for (int base = 0; base < kC; base += 256) {
+    const int v = ksz[(size_t)h * kC + base + tid];
+    int tot;
+    const int ex = block_excl_scan_256(v, ws, tot);
+    pv.k_off[(size_t)h * (kC + 1) + base + tid] = running + ex;
+    running += tot;
+  }
+  if (tid == 0) pv.k_off[(size_t)h * (kC + 1) + kC] = running;
+
+  // tasks of the heads before this one, so the task array is head-major
+  int gbase = 0, ntask = 0;
+  for (int hh = 0; hh <= h; ++hh) {
+    int cnt = 0;
+    for (int c = tid; c < CQ; c += 256) cnt += cdiv(qsz[(size_t)hh * CQ + c], QT);
+    int tot;
+    block_excl_scan_256(cnt, ws, tot);
+    if (hh < h) gbase += tot; else ntask = tot;
+  }
+  if (h == H - 1 && tid == 0) pv.counters[0] = gbase + ntask;
+
+  int qrun = 0, trun = 0;
+  unsigned long long pairs = 0;
+  for (int base = 0; base < CQ; base += 256) {
+    const int c = base + tid;
+    const int v = c < CQ ? qsz[(size_t)h * CQ + c] : 0;
+    const int nt = cdiv(v, QT);
+    int totq, tott;
+    const int exq = block_excl_scan_256(v, ws, totq);
+    const int ext = block_excl_scan_256(nt, ws, tott);
+    int s = qrun + exq;
+    for (int i = 0; i < nt; ++i) {
+      const int rows = v / nt + (i < v % nt ? 1 : 0);
+      pv.tasks[gbase + trun + ext + i] = make_int4(h, c, s, rows);
+      s += rows;
+    }
+    if (c < CQ) pairs += (unsigned long long)v * (unsigned long long)pv.kv_lens[(size_t)h * CQ + c];
+    qrun += totq;
+    trun += tott;
+  }
+  atomicAdd(reinterpret_cast<unsigned long long*>(pv.counters + 2), pairs);
+  __syncthreads();
+  if (ntask > PLAN_SORT_MAX || ntask < 2) return;
+
+  int P2 = 2;
+  while (P2 < ntask) P2 <<= 1;
+  for (int i = tid; i < P2; i += 256) {
+    unsigned long long key = 0ull;
+    if (i < ntask) {
+      const int4 tk = pv.tasks[gbase + i];
+      unsigned long long work = (unsigned long long)tk.w * (unsigned long long)pv.kv_lens[(size_t)h * CQ + tk.y];
+      if (work > 0xFFFFFFFFull) work = 0xFFFFFFFFull;
+      key = (work << 32) | (unsigned long long)(0x7FFFFFFF - i);
+    }
+    skey[i] = key;
+  }
+  __syncthreads();
+  for (int k = 2; k <= P2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = tid; i < P2; i += 256) {
+        const int ixj = i ^ j;
+        if (ixj > i) {
+          const unsigned long long a = skey[i], b = skey[ixj];
+          const bool desc = (i & k) == 0;
+          if (desc ? (a < b) : (a > b)) { skey[i] = b; skey[ixj] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+  int4 mine[PLAN_SORT_MAX / 256];
+  int n = 0;
+  for (int i = tid; i < ntask; i += 256) mine[n++] = pv.tasks[gbase + (0x7FFFFFFF - (int)(skey[i] & 0xFFFFFFFFull))];
+  __syncthreads();
+  n = 0;
+  for (int i = tid; i < ntask; i += 256) pv.tasks[gbase + i] = mine[n++];
+}
+
+__global__ void plan_info_kernel(const int* __restrict__ counters, int* __restrict__ info) {
+  if (threadIdx.x < 4) info[threadIdx.x] = threadIdx.x == 0 ? counters[0] : (threadIdx.x < 3 ? counters[threadIdx.x + 1] : 0);
+}
+
+// ---------------------------------------------------------------------------
+// shared pieces of the two tensor-core kernels
+// ---------------------------------------------------------------------------
+struct RowState {
+  float m;      // reference maximum (log2 domain) the stored P and O are relative to
+  float l;      // running denominator
+};
+
+constexpr float kLazy = 8.0f;   // rescale O only when the row maximum grows by more than 2^8
+
+// Rescale the fp32 accumulator rows in TMEM by `alpha` (per thread = per row).
+__device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tO_lane + c * 32, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+    tmem_st32(tO_lane + c * 32, v);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// exact attention over the unions
+// ---------------------------------------------------------------------------
+constexpr int AT_TILE = KT * kD * 2;   // 32 KB
+constexpr int AT_SMEM_INTS = 2 * KT + 2 * MAX_RUNS + 8 + 32;
+constexpr int AT_SMEM = 3 * AT_TILE + 64 + AT_SMEM_INTS * 4 + 1024;
+
+__global__ void __launch_bounds__(128, 2) attn_kernel(
+    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp,
+    const uint32_t* __restrict__ ub, const int* __restrict__ qperm, __nv_bfloat16* __restrict__ attn_out,
+    float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 2 * AT_TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 3 * AT_TILE);          // [0] S ready, [1] O ready
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + 3 * AT_TILE + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + 3 * AT_TILE + 32);
+  int* sInt = reinterpret_cast<int*>(sm + 3 * AT_TILE + 64);
+  int* sGidx = sInt;                    // [2][KT] row of kp/vp for every key slot of a tile, -1 past the end
+  int* sRunStart = sInt + 2 * KT;       // [MAX_RUNS]
+  int* sRunCum = sRunStart + MAX_RUNS;  // [MAX_RUNS + 1]
+  int* sMisc = sRunCum + MAX_RUNS + 8;  // [0] task, [1] runs; scan scratch from [8]
+
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bars + 0, 1);
+    mbar_init(bars + 1, 1);
+    mbar_init_fence();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
+  uint32_t phS = 0, phO = 0;
+  const int numTasks = pv.counters[0];
+  const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
+  constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
+
+  const int ld_ch = tid & 15, ld_r0 = tid >> 4;
+  const uint32_t ld_blk = (ld_ch >> 3) * (KT * 128);   // 64-column block of this thread's chunk
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) sMisc[0] = atomicAdd(&pv.counters[1], 1);
+    __syncthreads();
+    const int ti = sMisc[0];
+    if (ti >= numTasks || *abort_flag) break;
+    const int4 tk = pv.tasks[ti];
+    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
+    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
+    const size_t rowbase = (size_t)h * N + qs;
+
+    if (kvlen == 0) {   // empty union: O = 0, lse = -inf
+      for (int i = tid; i < qrows * 16; i += 128)
+        reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
+      for (int r = tid; r < qrows; r += 128) attn_lse[rowbase + r] = -INFINITY;
+      continue;
+    }
+
+    // ---- Q tile, gathered through qperm --------------------------------------
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int r = ld_r0 + 8 * u;
+      const bool valid = r < qrows;
+      const int orig = qperm[rowbase + (valid ? r : 0)];
+      cp_async16(sQ + ld_blk + sw128(r, ld_ch & 7), q + ((size_t)h * N + orig) * kD + ld_ch * 8,
+                 valid ? 16u : 0u);
+    }
+    cp_async_commit();
+
+    // ---- runs of selected, non-empty key clusters -----------------------------
+    {
+      const int* koh = pv.k_off + (size_t)h * (kC + 1);
+      const uint32_t* ubr = ub + ((size_t)h * CQ + qc) * (kC / 32);
+      const int c0 = tid * 16;
+      const uint32_t bw = (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu;
+      const int base0 = koh[c0];
+      bool pne0 = false;
+      if (c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
+      int offs[17];
+      offs[0] = base0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
+      int cnt = 0, sz = 0;
+      {
+        bool pne = pne0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+          if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
+          pne = cne;
+        }
+      }
+      // 128-thread exclusive scans of (cnt, sz)
+      int* ws = sMisc + 8;
+      const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
+      if (lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
+      __syncthreads();
+      int kbase = ic - cnt, pbase = is - sz;
+      for (int w = 0; w < warp; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
+      const int totc = ws[0] + ws[1] + ws[2] + ws[3];
+      if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
+        if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
+      } else {
+        bool pne = pne0;
+        int k = kbase, p = pbase;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+          if (cne) {
+            if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
+            p += offs[j + 1] - offs[j];
+          }
+          pne = cne;
+        }
+        if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
+      }
+      __syncthreads();
+      if (*abort_flag) break;
+    }
+    const int nruns = sMisc[1];
+    const int ntiles = cdiv(kvlen, KT);
+
+    auto key_row = [&](int p) -> int {   // kp/vp row of the p-th token of the union
+      if (p >= kvlen) return -1;
+      int lo = 0, hi = nruns - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sRunCum[mid] <= p) lo = mid; else hi = mid - 1;
+      }
+      return sRunStart[lo] + p - sRunCum[lo];
+    };
+    auto load_tile = [&](uint32_t dst, const __nv_bfloat16* src, const int* gidx) {
+      const __nv_bfloat16* sb = src + (size_t)h * N * kD + ld_ch * 8;
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        const int r = ld_r0 + 8 * u;
+        const int g = gidx[r];
+        cp_async16(dst + ld_blk + sw128(r, ld_ch & 7), sb + (size_t)(g < 0 ? 0 : g) * kD, g < 0 ? 0u : 16u);
+      }
+      cp_async_commit();
+    };
+
+    sGidx[tid] = key_row(tid);
+    sGidx[KT + tid] = key_row(KT + tid);
+    __syncthreads();
+    load_tile(sK, kp, sGidx);
+
+    RowState rs;
+    rs.m = -INFINITY;
+    rs.l = 0.f;
+    bool dead = false;
+
+    for (int t = 0; t < ntiles; ++t) {
+      const int* gcur = sGidx + (t & 1) * KT;
+      const int* gnxt = sGidx + ((t + 1) & 1) * KT;
+      cp_async_wait<0>();          // Q (first tile) and K(t) have landed
+      fence_proxy_async();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
+          const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
+          umma_ss(tS, ad, bd, idescQK, s > 0 ? 1u : 0u);
+        }
+        umma_commit(bars + 0);
+      }
+      if (!mbar_wait(bars + 0, phS, abort_flag)) { dead = true; break; }
+      phS ^= 1u;
+      if (t > 0) {
+        if (!mbar_wait(bars + 1, phO, abort_flag)) { dead = true; break; }
+        phO ^= 1u;
+      }
+      tc_fence_after();
+      // K tile and V tile buffers are free now
+      load_tile(sV, vp, gcur);
+      const bool more = t + 1 < ntiles;
+      if (more) load_tile(sK, kp, gnxt);
+
+      // ---- softmax of this thread's row --------------------------------------
+      float s[KT];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS_lane + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) s[c * 32 + j] = __uint_as_float(v[j]);
+      }
+      const int valid = kvlen - t * KT;
+      if (valid < KT) {
+#pragma unroll
+        for (int j = 0; j < KT; ++j) if (j >= valid) s[j] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int j = 1; j < KT; ++j) mx = fmaxf(mx, s[j]);
+      mx *= sc;
+      if (t == 0) {
+        rs.m = mx;
+      } else {
+        const bool grow = mx > rs.m + kLazy;
+        if (__any_sync(0xffffffffu, grow)) {
+          const float mnew = grow ? mx : rs.m;
+          const float alpha = ex2_approx(rs.m - mnew);
+          rescale_rows(tO_lane, alpha);
+          rs.l *= alpha;
+          rs.m = mnew;
+        }
+      }
+      const float nm = -rs.m;
+      float lsum = 0.f;
+      uint32_t pk[KT / 2];
+#pragma unroll
+      for (int j = 0; j < KT / 2; ++j) {
+        const float p0 = ex2_approx(fmaf(s[2 * j], sc, nm));
+        const float p1 = ex2_approx(fmaf(s[2 * j + 1], sc, nm));
+        lsum += p0 + p1;
+        pk[j] = pack_bf2(p0, p1);
+      }
+      rs.l += lsum;
+      {
+        uint32_t lo[32], hi[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { lo[j] = pk[j]; hi[j] = pk[32 + j]; }
+        tmem_st32(tS_lane, lo);
+        tmem_st32(tS_lane + 32, hi);
+      }
+      tmem_wait_st();
+      if (more) cp_async_wait<1>(); else cp_async_wait<0>();   // V(t) has landed
+      fence_proxy_async();
+      tc_fence_before();
+      __syncthreads();
+      if (tid == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int s8 = 0; s8 < 8; ++s8) {
+          const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
+          umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+        }
+        umma_commit(bars + 1);
+      }
+      // rows of tile t + 2 replace those of tile t
+      if (t + 2 < ntiles) sGidx[(t & 1) * KT + tid] = key_row((t + 2) * KT + tid);
+    }
+    if (!dead) {
+      if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
+      else phO ^= 1u;
+    }
+    if (dead) break;
+    tc_fence_after();
+    {
+      const float inv = 1.0f / rs.l;
+      const bool wr = tid < qrows;
+      uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + tid) * kD);
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tO_lane + c * 32, v);
+        tmem_wait_ld();
+        if (wr) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_bf2(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+            o.y = pack_bf2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+            o.z = pack_bf2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+            o.w = pack_bf2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+            dst[c * 4 + g] = o;
+          }
+        }
+      }
+      if (wr) attn_lse[rowbase + tid] = (rs.m + log2f(rs.l)) * 0.6931471805599453f;
+    }
+    tc_fence_before();
+  }
+  if (*abort_flag && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------
+// centroid residual + merge, 128 sorted queries per CTA
+// ---------------------------------------------------------------------------
+constexpr int TL_Q = 128;
+constexpr int TL_C = 128;                 // centroids per tile
+constexpr int TL_SQ = TL_Q * 128;         // 16 KB: QU rows padded to 128 B
+constexpr int TL_SC = TL_C * 128;         // 16 KB: cks rows padded to 128 B
+constexpr int TL_SV = TL_C * kD * 2;      // 32 KB
+constexpr int TL_SMEM_USED = TL_SQ + TL_SC + TL_SV + 64 + TL_C * 4 + 1024;
+// padded so that at most two CTAs share an SM: tensor memory holds two 256-column allocations
+constexpr int TL_SMEM = TL_SMEM_USED > 80 * 1024 ? TL_SMEM_USED : 80 * 1024;
+
+__global__ void __launch_bounds__(128, 2) tail_kernel(
+    const __nv_bfloat16* __restrict__ attn_out, const float* __restrict__ attn_lse,
+    const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
+    const __nv_bfloat16* __restrict__ sumv, const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
+    const int* __restrict__ qlab, const int* __restrict__ qperm, const float* __restrict__ lam_s,
+    const float* __restrict__ tailw_ptr, __nv_bfloat16* __restrict__ out, int N, int CQ,
+    int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base, sC = base + TL_SQ, sV = base + TL_SQ + TL_SC;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + TL_SQ + TL_SC + TL_SV);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + TL_SQ + TL_SC + TL_SV + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + TL_SQ + TL_SC + TL_SV + 32);
+  float* sCnt = reinterpret_cast<float*>(sm + TL_SQ + TL_SC + TL_SV + 64);
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int h = blockIdx.y, qs = blockIdx.x * TL_Q;
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    mbar_init(bars + 0, 1);
+    mbar_init(bars + 1, 1);
+    mbar_init_fence();
+  }
+  const int j = qs + tid;
+  const bool active = j < N;
+  const int orig = active ? qperm[(size_t)h * N + j] : 0;
+  const int label = active ? qlab[(size_t)h * N + orig] : 0;
+  const uint32_t* mrow = ub + ((size_t)h * CQ + label) * (kC / 32);
+
+  // QU rows of the 128 sorted queries: 64 B each, 4 chunks, into 128-byte rows
+  {
+    const int ch = tid & 3, r0 = tid >> 2;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + 32 * u;
+      const bool valid = qs + r < N;
+      const int o = valid ? qperm[(size_t)h * N + qs + r] : 0;
+      cp_async16(sQ + sw128(r, ch), QU + ((size_t)h * N + o) * kR + ch * 8, valid ? 16u : 0u);
+    }
+    cp_async_commit();
+  }
+  auto load_c = [&](int tile) {   // centroid tile: 128 rows x 64 B
+    const int ch = tid & 3, r0 = tid >> 2;
+    const __nv_bfloat16* src = cks + ((size_t)h * kC + tile * TL_C) * kR + ch * 8;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + 32 * u;
+      cp_async16(sC + sw128(r, ch), src + (size_t)r * kR, 16u);
+    }
+    cp_async_commit();
+  };
+  auto load_v = [&](int tile) {   // value-sum tile: 128 rows x 256 B
+    const int ch = tid & 15, r0 = tid >> 4;
+    const __nv_bfloat16* src = sumv + ((size_t)h * kC + tile * TL_C) * kD + ch * 8;
+#pragma unroll
+    for (int u = 0; u < 16; ++u) {
+      const int r = r0 + 8 * u;
+      cp_async16(sV + (ch >> 3) * (TL_C * 128) + sw128(r, ch & 7), src + (size_t)r * kD, 16u);
+    }
+    cp_async_commit();
+  };
+  load_c(0);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+  const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
+  constexpr uint32_t idescS = make_idesc_bf16(128, TL_C, false, false);
+  constexpr uint32_t idescT = make_idesc_bf16(128, kD, false, true);
+  constexpr float LOG2E = 1.4426950408889634f;
+  constexpr int NT = kC / TL_C;
+
+  uint32_t phS = 0, phO = 0;
+  float m = -INFINITY, phi = 0.f;     // m in log2 units
+  bool any_tile = false;              // has any PV product been accumulated yet
+  bool dead = false;
+
+  for (int t = 0; t < NT; ++t) {
+    cp_async_wait<0>();
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const uint64_t ad = make_sdesc(sQ + s * 32, 16, 1024);
+        const uint64_t bd = make_sdesc(sC + s * 32, 16, 1024);
+        umma_ss(tS, ad, bd, idescS, s > 0 ? 1u : 0u);
+      }
+      umma_commit(bars + 0);
+    }
+    sCnt[tid] = (float)ksz[(size_t)h * kC + t * TL_C + tid];
+    const uint4 mw4 = *reinterpret_cast<const uint4*>(mrow + t * 4);
+    if (!mbar_wait(bars + 0, phS, abort_flag)) { dead = true; break; }
+    phS ^= 1u;
+    if (t > 0) {
+      if (!mbar_wait(bars + 1, phO, abort_flag)) { dead = true; break; }
+      phO ^= 1u;
+    }
+    tc_fence_after();
+    load_v(t);
+    const bool more = t + 1 < NT;
+    if (more) load_c(t + 1);
+    __syncthreads();     // sCnt visible
+
+    float s[TL_C];
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      tmem_ld32(tS_lane + c * 32, v);
+      tmem_wait_ld();
+#pragma unroll
+      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
+    }
+    const uint32_t mw[4] = {mw4.x, mw4.y, mw4.z, mw4.w};
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < TL_C; ++i) {
+      // the score is rounded to fp16 exactly as the selection saw it
+      const float g = __half2float(__float2half_rn(s[i])) * LOG2E;
+      s[i] = ((mw[i >> 5] >> (i & 31)) & 1u) ? -INFINITY : g;
+      mx = fmaxf(mx, s[i]);
+    }
+    const bool grow = mx > m + kLazy || (m == -INFINITY && mx > -INFINITY);
+    if (__any_sync(0xffffffffu, grow)) {
+      const float mnew = grow ? mx : m;
+      const float alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mnew);
+      if (any_tile) rescale_rows(tO_lane, alpha);
+      phi *= alpha;
+      m = mnew;
+    }
+    const float nm = (m == -INFINITY) ? 0.f : -m;
+    float ps = 0.f;
+    uint32_t pk[TL_C / 2];
+#pragma unroll
+    for (int i = 0; i < TL_C / 2; ++i) {
+      const float p0 = ex2_approx(s[2 * i] + nm);
+      const float p1 = ex2_approx(s[2 * i + 1] + nm);
+      ps = fmaf(p0, sCnt[2 * i], ps);
+      ps = fmaf(p1, sCnt[2 * i + 1], ps);
+      pk[i] = pack_bf2(p0, p1);
+    }
+    phi += ps;
+    {
+      uint32_t lo[32], hi[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { lo[i] = pk[i]; hi[i] = pk[32 + i]; }
+      tmem_st32(tS_lane, lo);
+      tmem_st32(tS_lane + 32, hi);
+    }
+    tmem_wait_st();
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (tid == 0) {
+      tc_fence_after();
+#pragma unroll
+      for (int s8 = 0; s8 < 8; ++s8) {
+        const uint64_t bd = make_sdesc(sV + s8 * 2048, TL_C * 128, 1024);
+        umma_ts(tO, tS + s8 * 8, bd, idescT, (t > 0 || s8 > 0) ? 1u : 0u);
+      }
+      umma_commit(bars + 1);
+    }
+    any_tile = true;
+  }
+  if (!dead) {
+    if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
+  }
+  tc_fence_after();
+  if (!dead) {
+    // merge with the exact part (natural-log units from here on); rows past N
+    // only take part in the warp-collective TMEM loads
+    const float lam = lam_s[h], tw = *tailw_ptr;
+    const float mt = (m == -INFINITY) ? 0.f : m * 0.6931471805599453f;
+    const float le = active ? attn_lse[(size_t)h * N + j] : 0.f;
+    float ex, st;
+    if (le >= mt) { ex = 1.0f; st = __expf(mt - le); } else { ex = __expf(le - mt); st = 1.0f; }
+    const float ph = st * phi;
+    const bool bad = ph <= 1.0e-6f * ex;
+    const float inv = 1.0f / fmaxf(ex + ph * tw, 1.0e-12f);
+    const float we = bad ? 1.0f : ex * inv;
+    const float wt = bad ? 0.0f : st * tw * lam * inv;
+    const uint4* src = reinterpret_cast<const uint4*>(attn_out + ((size_t)h * N + (active ? j : 0)) * kD);
+    uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)h * N + orig) * kD);
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      uint32_t v[32];
+      tmem_ld32(tO_lane + c * 32, v);
+      tmem_wait_ld();
+      if (active) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const uint4 e = src[c * 4 + g];
+          uint4 o;
+          if (bad) {
+            o = e;
+          } else {
+            o.x = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 0]), we * bf_lo(e.x)), fmaf(wt, __uint_as_float(v[8 * g + 1]), we * bf_hi(e.x)));
+            o.y = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 2]), we * bf_lo(e.y)), fmaf(wt, __uint_as_float(v[8 * g + 3]), we * bf_hi(e.y)));
+            o.z = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 4]), we * bf_lo(e.z)), fmaf(wt, __uint_as_float(v[8 * g + 5]), we * bf_hi(e.z)));
+            o.w = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 6]), we * bf_lo(e.w)), fmaf(wt, __uint_as_float(v[8 * g + 7]), we * bf_hi(e.w)));
+          }
+          dst[c * 4 + g] = o;
+        }
+      }
+    }
+  }
+  if (dead && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace t2t
+
+using namespace t2t;
+
+extern "C" size_t t2t_tile_attn_plan_ints(int H, int N, int CQ) {
+  return plan_task_offset(H) + 4 * plan_max_tasks(H, N, CQ) + (size_t)H * CQ;
+}
+
+extern "C" size_t t2t_tile_attn_ws_bytes(int H, int N) {
+  return (((size_t)H * N * kD * 2 + 255) & ~(size_t)255) + (size_t)H * N * 4;
+}
+
+extern "C" int t2t_tile_attn(const void* q, const void* kp, const void* vp, const void* tile_sizes,
+                             const void* kcounts, const void* unip, const void* QU, const void* cks,
+                             const void* sumv, const void* lam, const void* qlab, const void* qperm,
+                             const float* tailw, void* out, int* plan, int rebuild_plan, int H, int N, int CQ,
+                             void* ws, size_t ws_bytes, int* d_status, cudaStream_t st) {
+  if (!q || !kp || !vp || !tile_sizes || !kcounts || !unip || !QU || !cks || !sumv || !lam || !qlab || !qperm ||
+      !tailw || !out || !plan || !ws)
+    return T2T_ERR_ARG;
+  if (H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  __nv_bfloat16* attn_out = (__nv_bfloat16*)ws;
+  float* attn_lse = (float*)((char*)ws + (((size_t)H * N * kD * 2 + 255) & ~(size_t)255));
+  const PlanView pv = plan_view(plan, H, N, CQ);
+
+  if (rebuild_plan) {
+    if (cudaMemsetAsync(pv.counters, 0, PLAN_HDR * sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
+    kvlen_kernel<<<dim3(cdiv(CQ, 8), H), 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts,
+                                                       (const uint32_t*)unip, pv.kv_lens, CQ);
+    plan_kernel<<<H, 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts, H, N, CQ, plan);
+  } else {
+    if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
+  }
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+      cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
+    return T2T_ERR_CUDA;
+  attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kp,
+                                             (const __nv_bfloat16*)vp, (const uint32_t*)unip, (const int*)qperm,
+                                             attn_out, attn_lse, plan, H, N, CQ, d_status);
+  tail_kernel<<<dim3(cdiv(N, TL_Q), H), 128, TL_SMEM, st>>>(
+      attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const __nv_bfloat16*)sumv,
+      (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
+      (__nv_bfloat16*)out, N, CQ, d_status);
+  return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}
+
+extern "C" int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, int* d_info, cudaStream_t st) {
+  if (!plan || !d_info) return T2T_ERR_ARG;
+  const PlanView pv = plan_view(const_cast<int*>(plan), H, N, CQ);
+  plan_info_kernel<<<1, 32, 0, st>>>(pv.counters, d_info);
+  return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}

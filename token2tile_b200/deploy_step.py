@@ -1,0 +1,335 @@
+"""Token2Tile attention operator for B200: one sparse attention call of one layer.
+
+Host-side mirror of the reference operator module
+(token2tile/operator/deploy_step.py): same class, constructor arguments,
+methods, attributes and rebuild / reuse rules, over the sm_100a kernels of
+libt2t_b200.so.  `MaskedStepDeploy.step(q, k, v, state)` runs, for q, k, v of
+shape [H, N, 128] (bfloat16):
+
+  1. projection   Q -> Q Uq, K -> K Uk into the rank-32 space      t2t_project
+  2. clustering   warm-started k-means of keys (2048 clusters) and
+                  queries (CQ clusters), stable grouping, cluster-
+                  major V and per-cluster value sums                t2t_kmeans_maintain
+  3. scoring +    every query against every key centroid, budgeted
+     selection    prefix of whole clusters, union per query cluster t2t_score_select_union
+  4. attention    exact attention of every query cluster over its
+                  union + centroid residual, one softmax            t2t_tile_attn
+
+PyTorch supplies device memory, streams and the two tiny factorisations of the
+projection fit; every stage above is a hand-written CUDA kernel.  There is no
+CPU path: the module refuses to load without the compiled library.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from ._lib import check, ptr
+
+BF16 = torch.bfloat16
+
+
+# ---------------------------------------------------------------------------
+# low-rank space
+# ---------------------------------------------------------------------------
+
+def _eigh_robust(M):
+    """Symmetric eigendecomposition with the reference's fall-back to the CPU
+    when the device solver does not converge (deploy_step.py:104-111)."""
+    try:
+        return torch.linalg.eigh(M)
+    except torch._C._LinAlgError:
+        e, V = torch.linalg.eigh(M.cpu())
+        return e.to(M.device), V.to(M.device)
+
+
+def _svd_robust(M):
+    try:
+        return torch.linalg.svd(M)
+    except torch._C._LinAlgError:
+        U, S, Vh = torch.linalg.svd(M.cpu())
+        return U.to(M.device), S.to(M.device), Vh.to(M.device)
+
+
+def online_u(qf, kf, r=32):
+    """Matched rank-r projections Uq, Uk [H, D, r] (fp32) minimising
+    ||Q K^T - (Q Uq)(K Uk)^T||_F (deploy_step.py:122-149): with second moments
+    Mq, Mk and the SVD Mq^(1/2) Mk^(1/2) = U S V^T, Uq = Mq^(-1/2) U_r S_r^(1/2)
+    and Uk = Mk^(-1/2) V_r S_r^(1/2).  All factorisations run in fp64."""
+    for name, t in (("q", qf), ("k", kf)):
+        bad = ~torch.isfinite(t)
+        if bool(bad.any()):
+            raise RuntimeError(
+                f"online_u: non-finite {name} input; per-head counts "
+                f"{bad.sum(dim=(1, 2)).tolist()}, shape {tuple(t.shape)}")
+    Uqs, Uks = [], []
+    for h in range(qf.shape[0]):
+        q, k = qf[h].double(), kf[h].double()
+        Mq = (q.T @ q) / q.shape[0]
+        Mk = (k.T @ k) / k.shape[0]
+        eq, Vq = _eigh_robust(Mq)
+        ek, Vk = _eigh_robust(Mk)
+        eq = eq.clamp_min(1e-8)
+        ek = ek.clamp_min(1e-8)
+        Rq = Vq @ torch.diag(eq.sqrt()) @ Vq.T
+        Rk = Vk @ torch.diag(ek.sqrt()) @ Vk.T
+        Rqi = Vq @ torch.diag(eq.rsqrt()) @ Vq.T
+        Rki = Vk @ torch.diag(ek.rsqrt()) @ Vk.T
+        U, S, Vh = _svd_robust(Rq.T @ Rk)
+        sr = S[:r].sqrt()
+        Uqs.append((Rqi.T @ U[:, :r] * sr).float())
+        Uks.append((Rki @ Vh[:r].T * sr).float())
+    return torch.stack(Uqs), torch.stack(Uks)
+
+
+def _stream_ptr(stream) -> int:
+    return stream.cuda_stream
+
+
+class MaskedStepDeploy:
+    """Persistent buffers and kernels for one (H, N, C_Q) attention shape
+    (deploy_step.py:152-242).
+
+    s_frac: per-query token budget as a fraction of N; `ns_t` holds the token
+        count on the device and may be overwritten between calls.
+    mask_refresh: rebuild the structure every this many annotated steps.
+    cfg_reuse: reuse the structure across CFG branches even when
+        mask_refresh is 1.
+    pin_tail: the last pin_tail keys form one reserved key cluster that every
+        query executes exactly.
+    split_cap: accepted for interface compatibility; selection here works per
+        query row, so there is nothing to split."""
+
+    def __init__(self, H, N, CQ, *, C=2048, D=128, r=32, s_frac=0.05, tailw=1.0, device="cuda",
+                 mask_refresh=1, cfg_reuse=False, pin_tail=0, split_cap="auto"):
+        if C != 2048 or D != 128:
+            raise ValueError("the kernels require C=2048 and D=128")
+        if r != 32:
+            raise ValueError("the kernels require r=32")
+        if N < max(C, CQ):
+            raise ValueError("N must be at least max(C, CQ)")
+        self.lib = _lib.load()
+        self.H, self.N, self.CQ, self.C, self.D, self.r = H, N, CQ, C, D, r
+        self.ns = max(1, int(s_frac * N))
+        self.tailw = tailw
+        self.dev = dev = torch.device(device)
+        self.scale = 1.0 / math.sqrt(D)
+        self.pin_tail = int(pin_tail)
+        self.split_cap = 0
+
+        f32, i32 = torch.float32, torch.int32
+        e = lambda *shape, dtype: torch.empty(*shape, device=dev, dtype=dtype)
+        # persistent buffers, allocated once
+        self.QU = e(H, N, r, dtype=BF16)
+        self.KU = e(H, N, r, dtype=BF16)
+        self.rowcnt = e(H, N, dtype=i32)
+        self.kp = e(H, N, D, dtype=BF16)
+        self.vp = e(H, N, D, dtype=BF16)
+        self.tile_attn_out = e(H, N, D, dtype=BF16)
+        self._kmm_cq2 = e(H, CQ, r, dtype=BF16)
+        self._kmm_ck2 = e(H, C, r, dtype=f32)
+        self._kmm_sumv = e(H, C, D, dtype=BF16)
+        self._kmm_lam = e(H, dtype=f32)
+        self.tailw_t = torch.tensor(float(tailw), device=dev, dtype=f32)
+        self.ns_t = torch.tensor(self.ns, device=dev, dtype=i32)
+        self.status = torch.zeros(1, device=dev, dtype=i32)
+        L = self.lib
+        self._tile_attn_plan_ints = int(L.t2t_tile_attn_plan_ints(H, N, CQ))
+        ws = max(int(L.t2t_kmeans_maintain_ws_bytes(H, N, CQ, C)),
+                 int(L.t2t_vstats_gather_ws_bytes(H, C)),
+                 int(L.t2t_centroid_update_ws_bytes(H, N, C)))
+        self._ws = e(ws, dtype=torch.uint8)
+        self._attn_ws = e(int(L.t2t_tile_attn_ws_bytes(H, N)), dtype=torch.uint8)
+        self._struct = self._new_structure()      # structure of unannotated calls
+
+        # Structure reuse (deploy_step.py:210-221).  A full call (branch 0 and
+        # snapshot age >= mask_refresh) rebuilds the structure and stores it per
+        # key (layer); every other annotated call reuses the stored snapshot.
+        self.cfg_reuse = bool(cfg_reuse)
+        self.mask_refresh = max(1, int(mask_refresh))
+        self._cfg_on = self.cfg_reuse or self.mask_refresh > 1
+        self._cfg_hold = {}
+        self._cfg_parity = None
+        self._cfg_key = 0
+        self._cfg_step = 0
+
+        self.s_main = torch.cuda.Stream(device=dev)
+        self.s_side = torch.cuda.Stream(device=dev)
+        self.last_rebuilt = None
+
+    def _new_structure(self):
+        """Tensors that describe one structure (labels, groupings, centroids,
+        union, task plan); a snapshot owns one such set."""
+        H, N, CQ, C, r, dev = self.H, self.N, self.CQ, self.C, self.r, self.dev
+        i32 = torch.int32
+        e = lambda *shape, dtype: torch.empty(*shape, device=dev, dtype=dtype)
+        return {
+            "qlab": e(H, N, dtype=i32), "klab": e(H, N, dtype=i32),
+            "qperm": e(H, N, dtype=i32), "kperm": e(H, N, dtype=i32),
+            "tile_sizes": e(H, CQ, dtype=i32), "counts": e(H, C, dtype=i32),
+            "cks": e(H, C, r, dtype=BF16), "unip": e(H, CQ, C // 32, dtype=i32),
+            "tile_attn_plan": e(self._tile_attn_plan_ints, dtype=i32),
+            "Uq": None, "step": 0,
+        }
+
+    def _check_qkv(self, *tensors):
+        for t in tensors:
+            if t.dtype != BF16 or tuple(t.shape) != (self.H, self.N, self.D) or not t.is_contiguous() \
+                    or t.device != self.QU.device:
+                raise ValueError(
+                    f"expected contiguous bfloat16 [{self.H}, {self.N}, {self.D}] on {self.QU.device}, got "
+                    f"{t.dtype} {tuple(t.shape)} on {t.device}")
+
+    # -- kernel wrappers -------------------------------------------------------
+    def _project(self, x, U, out, st):
+        check(self.lib.t2t_project(ptr(x), ptr(U), ptr(out), self.H, self.N, ptr(self.status), st), "t2t_project")
+
+    def _assign(self, x, cen, labels, st):
+        check(self.lib.t2t_assign(ptr(x), ptr(cen), ptr(labels), self.H, self.N, cen.shape[1], -1, 0, st),
+              "t2t_assign")
+
+    def _centroid_update(self, x, labels, old, st):
+        newc = torch.empty_like(old)
+        counts = torch.empty(self.H, old.shape[1], device=self.dev, dtype=torch.int32)
+        check(self.lib.t2t_centroid_update(ptr(x), ptr(labels), ptr(old), ptr(newc), ptr(counts), self.H, self.N,
+                                           old.shape[1], ptr(self._ws), self._ws.numel(), st), "t2t_centroid_update")
+        return newc, counts
+
+    # -- state init ------------------------------------------------------------
+    def init_state(self, q, k, *, warm_iters=4, seed=0):
+        """Projections and initial centroids of one layer (deploy_step.py:245-266).
+        The projections are kept for the whole request; the centroids warm-start
+        every rebuild.  The warm Lloyd iterations use the exact assignment kernel
+        and the deterministic fixed-point centroid update."""
+        self._check_qkv(q, k)
+        N, r = self.N, self.r
+        Uq, Uk = online_u(q.float(), k.float(), r)
+        Uq = Uq.to(BF16).contiguous()
+        Uk = Uk.to(BF16).contiguous()
+        st = _stream_ptr(torch.cuda.current_stream(self.dev))
+        KU = torch.empty_like(self.KU)
+        QU = torch.empty_like(self.QU)
+        self._project(k, Uk, KU, st)
+        self._project(q, Uq, QU, st)
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        ik = torch.randperm(N, generator=g)[: self.C].sort().values.to(self.dev)
+        iq = torch.randperm(N, generator=g)[: self.CQ].sort().values.to(self.dev)
+        ck = KU[:, ik, :].contiguous()
+        cq = QU[:, iq, :].contiguous()
+        lab = torch.empty(self.H, N, device=self.dev, dtype=torch.int32)
+        for _ in range(warm_iters):
+            self._assign(KU, ck, lab, st)
+            ck, _ = self._centroid_update(KU, lab, ck, st)
+            self._assign(QU, cq, lab, st)
+            cq, _ = self._centroid_update(QU, lab, cq, st)
+        torch.cuda.synchronize(self.dev)
+        return {"Uq": Uq, "Uk": Uk, "ck": ck.contiguous(), "cq": cq.contiguous()}
+
+    def set_cfg_call(self, parity, key=0, step=0):
+        """Annotate the next step() call (deploy_step.py:268-277): parity is the
+        CFG branch (0 = the branch allowed to rebuild), key the snapshot slot
+        (one per layer), step the denoising step.  A branch-0 call rebuilds when
+        step - snapshot_step >= mask_refresh."""
+        self._cfg_parity = int(parity)
+        self._cfg_key = key
+        self._cfg_step = int(step)
+
+    def reset_cfg_reuse(self):
+        """Drop all snapshots and any pending annotation (deploy_step.py:279-283)."""
+        self._cfg_hold.clear()
+        self._cfg_parity = None
+
+    def _pick(self):
+        """Rebuild / reuse decision (deploy_step.py:297-316).  Returns
+        (snapshot to reuse or None, structure tensors a rebuild writes)."""
+        snap = None
+        held = None
+        parity = self._cfg_parity
+        self._cfg_parity = None          # an unannotated call never consumes a stale annotation
+        if self._cfg_on and parity is not None:
+            held = self._cfg_hold.get(self._cfg_key)
+            age = None if held is None else self._cfg_step - held["step"]
+            refresh_due = age is None or age < 0 or age >= self.mask_refresh
+            if held is not None and age >= 0 and not (parity == 0 and refresh_due):
+                snap = held
+            if snap is None:
+                # a rebuild overwrites the tensors of the snapshot it replaces
+                target = held if held is not None else self._new_structure()
+                return None, target, True
+        return snap, self._struct, False
+
+    # -- the attention call ------------------------------------------------------
+    def step(self, q, k, v, state):
+        """q, k, v: [H, N, 128] bfloat16 contiguous, original row order.  state:
+        dict(Uq, Uk, ck, cq); ck / cq are replaced by the centroids that
+        warm-start the next call.  Returns out [H, N, 128] bfloat16, a buffer
+        owned by the operator and overwritten by the next call."""
+        self._check_qkv(q, k, v)
+        caller = torch.cuda.current_stream(self.dev)
+        if caller != self.s_main:
+            self.s_main.wait_stream(caller)
+        H, N, C, CQ = self.H, self.N, self.C, self.CQ
+        L = self.lib
+        snap, S, publish = self._pick()
+        st = _stream_ptr(self.s_main)
+        with torch.cuda.stream(self.s_main):
+            if snap is None:
+                self._project(q, state["Uq"], self.QU, st)
+                self._project(k, state["Uk"], self.KU, st)
+                ck16 = torch.empty(H, C, self.r, device=self.dev, dtype=BF16)
+                check(L.t2t_kmeans_maintain(
+                    ptr(self.QU), ptr(self.KU), ptr(v), ptr(state["cq"]), ptr(state["ck"]),
+                    ptr(S["qlab"]), ptr(self._kmm_cq2), ptr(S["klab"]), ptr(self._kmm_ck2), ptr(ck16),
+                    ptr(S["cks"]), ptr(S["tile_sizes"]), ptr(S["qperm"]), ptr(S["counts"]), ptr(S["kperm"]),
+                    ptr(self.vp), ptr(self._kmm_sumv), ptr(self._kmm_lam), self.scale, H, N, CQ, C,
+                    self.pin_tail, ptr(self._ws), self._ws.numel(), st), "t2t_kmeans_maintain")
+                # fresh tensors, so the next call's inputs never alias kernel outputs
+                state["ck"] = ck16
+                state["cq"] = self._kmm_cq2.clone()
+                check(L.t2t_score_select_union(
+                    ptr(self.QU), ptr(S["cks"]), ptr(S["counts"]), ptr(S["qperm"]), ptr(S["tile_sizes"]),
+                    ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, st),
+                    "t2t_score_select_union")
+                S["Uq"] = state["Uq"]
+                S["step"] = self._cfg_step
+                if publish:
+                    self._cfg_hold[self._cfg_key] = S
+                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+            else:
+                S = snap
+                # a reuse call projects its queries with the snapshot's Uq so that
+                # QU and the stored centroids share a basis
+                self._project(q, S["Uq"], self.QU, st)
+                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+                check(L.t2t_vstats_gather(ptr(v), ptr(S["kperm"]), ptr(S["counts"]), ptr(self.vp),
+                                          ptr(self._kmm_sumv), ptr(self._kmm_lam), H, N, C, ptr(self._ws),
+                                          self._ws.numel(), st), "t2t_vstats_gather")
+            check(L.t2t_tile_attn(
+                ptr(q), ptr(self.kp), ptr(self.vp), ptr(S["tile_sizes"]), ptr(S["counts"]), ptr(S["unip"]),
+                ptr(self.QU), ptr(S["cks"]), ptr(self._kmm_sumv), ptr(self._kmm_lam), ptr(S["qlab"]),
+                ptr(S["qperm"]), ptr(self.tailw_t), ptr(self.tile_attn_out), ptr(S["tile_attn_plan"]),
+                1 if snap is None else 0, H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(),
+                ptr(self.status), st), "t2t_tile_attn")
+        self.last_rebuilt = snap is None
+        self.last_structure = S
+        # order the caller's stream after ours instead of a host sync
+        cur = torch.cuda.current_stream(self.dev)
+        cur.wait_stream(self.s_main)
+        cur.wait_stream(self.s_side)
+        return self.tile_attn_out
+
+    # -- diagnostics -------------------------------------------------------------
+    def device_status(self) -> int:
+        """Status word of the bounded device waits (synchronises)."""
+        return int(self.status.item())
+
+    def plan_info(self):
+        """(tasks, executed query-key pairs) of the structure used last (synchronises)."""
+        info = torch.zeros(4, device=self.dev, dtype=torch.int32)
+        st = _stream_ptr(torch.cuda.current_stream(self.dev))
+        check(self.lib.t2t_tile_attn_plan_info(ptr(self.last_structure["tile_attn_plan"]), self.H, self.N,
+                                               self.CQ, ptr(info), st), "t2t_tile_attn_plan_info")
+        a = info.cpu().tolist()
+        return a[0], (a[1] & 0xFFFFFFFF) | ((a[2] & 0xFFFFFFFF) << 32)
