@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the Token2Tile attention layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+
+Metric: milliseconds per attention layer at the Wan2.1-14B 720p shape
+(75,600 tokens x 40 heads x 128, bf16, 1.5 % budget, 512 query clusters).  A
+step is one full (structure-rebuilding) call of the layer; reuse calls and the
+1-rebuild-in-8 amortised figure are reported beside it.  With N GPUs the 40
+heads are split N ways (no traffic inside the operator); the value is the
+maximum over ranks, i.e. the whole-box time of the layer.
+
+Inputs are seeded synthetic tensors (token2tile_b200/synth.py); 2.3 GB of
+q/k/v per step is far larger than L2, so no flush is needed between steps.
+`--impl reference` times the CPU restatement of the operator (oracle/) on the
+host cores for one head per step and scales to 40 heads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+WORKLOAD = dict(name="wan2.1-14b-720p-self-attention-layer", H=40, grid="720p", N=75600, CQ=512, D=128,
+                s_frac=0.015)
+KERNELS_REBUILD = 2 + 18 + 1 + 1 + 2 + 2     # project, kmeans, select, gather, plan, attention + merge
+METRIC = "t2t_attn_ms_per_layer"
+UNIT = "ms/layer"
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=d["hbm_gbs"], tf_burst=d["bf16_tflops"], tf=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, tf_burst=1590.0, tf=1400.0, src="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return None
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        rows = [r.split(",") for r in Path(self.f.name).read_text().strip().splitlines() if r.count(",") >= 6]
+        os.unlink(self.f.name)
+        if not rows:
+            return None
+        try:
+            sm = sorted(float(r[0]) for r in rows)
+            reasons = []
+            for i, name in ((3, "hw_slowdown"), (4, "hw_thermal_slowdown"), (5, "sw_thermal_slowdown"),
+                            (6, "sw_power_cap")):
+                if any("Active" in r[i] and "Not" not in r[i] for r in rows):
+                    reasons.append(name)
+            return dict(sm_mhz=sm[len(sm) // 2], sm_max_mhz=float(rows[0][1]), samples=len(rows),
+                        power_w_max=max(float(r[2]) for r in rows), reasons=reasons)
+        except ValueError:
+            return None
+
+
+def time_events(fn, steps, stream=None):
+    """Device time of `steps` calls of fn, in ms, by CUDA events on the current stream."""
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def dense_attention_ms(q, k, v):
+    """Fastest dense attention on this box for the same tensors: median of 3
+    timed calls after 2 warm-ups, per library."""
+    import torch.nn.functional as F
+    out = {}
+    qb, kb, vb = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
+    cands = {}
+    try:
+        from torch.nn.attention import SDPBackend, sdpa_kernel
+        for name, be in (("sdpa_flash", SDPBackend.FLASH_ATTENTION), ("sdpa_cudnn", SDPBackend.CUDNN_ATTENTION)):
+            def run(be=be):
+                with sdpa_kernel([be]):
+                    return F.scaled_dot_product_attention(qb, kb, vb)
+            cands[name] = run
+    except ImportError:
+        pass
+    try:
+        from flash_attn import flash_attn_func
+        qf, kf, vf = (t.transpose(0, 1).unsqueeze(0).contiguous() for t in (q, k, v))
+        cands["flash_attn"] = lambda: flash_attn_func(qf, kf, vf)
+    except Exception:      # noqa: BLE001 - optional library
+        pass
+    for name, run in cands.items():
+        try:
+            for _ in range(2):
+                run()
+            ts = sorted(time_events(run, 1) for _ in range(3))
+            out[name] = ts[1]
+        except Exception as exc:      # noqa: BLE001 - a backend may refuse the shape
+            out[name] = None
+            print(f"[bench] dense backend {name} unavailable: {type(exc).__name__}", file=sys.stderr)
+    return out
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle on the host cores, one head per step
+# ---------------------------------------------------------------------------
+
+def cpu_head_step_factory(seed_head=0):
+    from oracle import t2t_oracle as O
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    O.FAST_DOT = True          # sgemm instead of the bit-exact chain: this leg is timed, not compared
+    W = WORKLOAD
+    torch.set_num_threads(os.cpu_count() or 1)
+    q, k, v = locality_mixture(1, GRIDS[W["grid"]], heads=[seed_head])
+    op = O.OracleOperator(1, W["N"], W["CQ"], s_frac=W["s_frac"])
+    state = op.init_state(q, k, warm_iters=1)
+
+    def step():
+        st = dict(state)
+        t0 = time.perf_counter()
+        op.step(q, k, v, st)
+        return (time.perf_counter() - t0) * 1e3 * W["H"]      # one head, scaled to the 40-head layer
+    return step, torch.get_num_threads()
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    step, cores = cpu_head_step_factory()
+    for _ in range(args.warmup):
+        step()
+    ts = [step() for _ in range(args.steps)]
+    val = sum(ts) / len(ts)
+    sample = "one head of 40 per step (full 75,600 tokens), time x 40"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": val, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD["name"], **{k: WORKLOAD[k] for k in ("H", "N", "CQ", "D", "s_frac")}},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def run_ours(args, rank, world, local_rank):
+    from token2tile_b200 import MaskedStepDeploy
+    from token2tile_b200.parallel import head_range
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    import torch.distributed as dist
+
+    W = WORKLOAD
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lo, hi = head_range(rank, world, W["H"])
+    Hl, N, CQ = hi - lo, W["N"], W["CQ"]
+    q, k, v = locality_mixture(Hl, GRIDS[W["grid"]], heads=range(lo, hi))
+    hq, hk, hv = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    qd, kd, vd = hq.to(dev), hk.to(dev), hv.to(dev)
+    hout = torch.empty(Hl, N, W["D"], dtype=torch.bfloat16).pin_memory()
+
+    op = MaskedStepDeploy(Hl, N, CQ, s_frac=W["s_frac"], device=dev, mask_refresh=1)
+    state0 = op.init_state(qd, kd, warm_iters=4, seed=0)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def maxr(x):
+        if world == 1:
+            return x
+        t = torch.tensor([x], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    state = dict(state0)
+
+    def rebuild_step():
+        op.step(qd, kd, vd, state)
+
+    for _ in range(args.warmup):
+        rebuild_step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = time_events(rebuild_step, args.steps)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ms_step = maxr(ms / args.steps)
+    assert op.device_status() == 0, "a device wait timed out"
+
+    # per-stage device times of one rebuild call
+    op.profile = True
+    rebuild_step()
+    stages = op.stage_times()
+    op.profile = False
+    tasks, pairs = op.plan_info()
+
+    # end to end: host buffers in, host buffer out, through the same call
+    def e2e_step():
+        qd.copy_(hq, non_blocking=True)
+        kd.copy_(hk, non_blocking=True)
+        vd.copy_(hv, non_blocking=True)
+        out = op.step(qd, kd, vd, state)
+        hout.copy_(out, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e2e_ms = maxr(time_events(e2e_step, max(2, args.steps // 2)) / max(2, args.steps // 2))
+    barrier()
+
+    # reuse calls (structure held, values recomputed)
+    opr = op
+    opr.mask_refresh, opr._cfg_on = 4, True
+    opr.set_cfg_call(0, key=0, step=0)
+    opr.step(qd, kd, vd, state)
+    cnt = [0]
+
+    def reuse_step():
+        cnt[0] += 1
+        opr.set_cfg_call(1, key=0, step=0)
+        opr.step(qd, kd, vd, state)
+
+    reuse_step()
+    barrier()
+    reuse_ms = maxr(time_events(reuse_step, max(2, args.steps // 2)) / max(2, args.steps // 2))
+    assert opr.last_rebuilt is False
+    op.profile = True
+    reuse_step()
+    reuse_stages = op.stage_times()
+    op.profile = False
+    barrier()
+
+    dense = dense_attention_ms(qd, kd, vd)
+    dense_ok = {n: t for n, t in dense.items() if t}
+    dense_best = maxr(min(dense_ok.values())) if dense_ok else None
+
+    pk = peaks()
+    flops = 4.0 * W["D"] * pairs
+    t_attn = stages.get("attn_exact", 0.0)
+    roofline = None
+    if t_attn > 0:
+        ach = flops / (t_attn * 1e-3) / 1e12
+        roofline = {"kernel": "attn_kernel", "bound": "tensor", "achieved": ach, "peak": pk["tf"],
+                    "unit": "TFLOP/s", "frac": ach / pk["tf"], "traffic": None, "peak_source": pk["src"] +
+                    " (sustained bf16 GEMM)", "flops_per_launch": flops, "ms_per_launch": t_attn,
+                    "executed_pair_fraction": pairs / (Hl * float(N) * N)}
+    B = 2
+    stage_bytes = {
+        "project": 2 * N * W["D"] * B * Hl + 2 * N * 32 * B * Hl,
+        "gather_k": 2 * N * W["D"] * B * Hl,
+        "kmeans": (6 * N * 32 * B + 2 * N * W["D"] * B + 10 * N * 4) * Hl,
+        "vstats": 2 * N * W["D"] * B * Hl,
+    }
+    stage_roof = {n: {"ms": stages[n], "algorithmic_GBps": stage_bytes[n] / (stages[n] * 1e-3) / 1e9,
+                      "frac_of_hbm_peak": stage_bytes[n] / (stages[n] * 1e-3) / 1e9 / pk["hbm"]}
+                  for n in stage_bytes if stages.get(n)}
+    tail_flops = float(N) * 2048 * (2 * 32 + 2 * W["D"]) * Hl
+    if stages.get("residual_merge"):
+        stage_roof["residual_merge"] = {"ms": stages["residual_merge"],
+                                        "TFLOPs": tail_flops / (stages["residual_merge"] * 1e-3) / 1e12,
+                                        "frac_of_tensor_peak": tail_flops / (stages["residual_merge"] * 1e-3) / 1e12 / pk["tf"]}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        step, cores = cpu_head_step_factory()
+        val = step()
+        cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+               "sample": "one head of 40 (full 75,600 tokens), one rebuild call, time x 40"}
+
+    if rank == 0:
+        amort = (ms_step + 7 * reuse_ms) / 8
+        bytes_in = 3 * Hl * N * W["D"] * 2
+        line = {
+            "metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": W["name"], "H": W["H"], "heads_per_gpu": Hl, "N": N, "CQ": CQ, "D": W["D"],
+                       "budget": W["s_frac"], "ns": op.ns, "call": "rebuild (mask_refresh=1)",
+                       "parallelism": f"head-parallel x{world}", "l2": "inputs (2.3 GB/step) exceed L2; no flush"},
+            "roofline": roofline, "cpu_baseline": cpu,
+            "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
+                    "d2h_bytes_per_step": Hl * N * W["D"] * 2},
+            "gpu_launches": KERNELS_REBUILD * args.steps, "clocks": clocks,
+            "reuse_ms": reuse_ms, "amortised_ms_1_rebuild_7_reuse": amort, "stages_ms": stages,
+            "reuse_stages_ms": reuse_stages, "stage_roofline": stage_roof, "tasks": tasks,
+            "dense_ms": dense, "fastest_dense_ms": dense_best,
+            "speedup_vs_dense": {"rebuild": dense_best / ms_step, "reuse": dense_best / reuse_ms,
+                                 "amortised": dense_best / amort} if dense_best else None,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+    else:
+        if args.warmup < 3:
+            args.warmup = 3
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

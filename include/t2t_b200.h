@@ -125,6 +125,21 @@ int t2t_tile_attn(const void* q, const void* kp, const void* vp, const void* til
                   const float* tailw, void* out, int* plan, int rebuild_plan, int H, int N, int CQ,
                   void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
 
+/* The three stages of t2t_tile_attn as separate calls (same arguments), so a
+ * caller can time or overlap them: the task plan (kv lengths, key-cluster
+ * offsets, tasks in longest-first order; selected_kv_lengths_kernel and
+ * plan_kernel, kernels/tile_attn/src/kernel.cu:259-378), the exact attention
+ * over the unions (attn_kernel, kernel.cu:820-1096) and the residual + merge
+ * (tail_wgmma_kernel, kernel.cu:1172-1450). */
+int t2t_tile_attn_plan(const void* tile_sizes, const void* kcounts, const void* unip, int* plan, int H, int N,
+                       int CQ, cudaStream_t stream);
+int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp, const void* unip, const void* qperm,
+                        int* plan, int H, int N, int CQ, void* ws, size_t ws_bytes, int* d_status,
+                        cudaStream_t stream);
+int t2t_tile_attn_merge(const void* QU, const void* cks, const void* sumv, const void* kcounts, const void* unip,
+                        const void* qlab, const void* qperm, const void* lam, const float* tailw, void* out,
+                        int H, int N, int CQ, void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
+
 /* Number of tasks and executed (query, key) pairs of the current plan, for
  * FLOP accounting: info[0] = tasks, info[1..2] = pairs as low/high 32 bits.
  * Device-side; copies 4 ints into d_info. */

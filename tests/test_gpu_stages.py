@@ -64,6 +64,7 @@ def _assign(lib, x, cen, pin_begin=-1, pin_label=0):
     H, N, _ = x.shape
     lab = torch.empty(H, N, dtype=torch.int32, device=DEV)
     _ok(lib.t2t_assign(x.data_ptr(), cen.data_ptr(), lab.data_ptr(), H, N, cen.shape[1], pin_begin, pin_label, _st()))
+    torch.cuda.synchronize()
     return lab
 
 
@@ -101,8 +102,10 @@ def test_centroid_update_bit_exact(lib, small_case):
     ws = torch.empty(lib.t2t_centroid_update_ws_bytes(H, N, 2048), dtype=torch.uint8, device=DEV)
     newc = torch.empty(H, 2048, 32, dtype=BF, device=DEV)
     counts = torch.empty(H, 2048, dtype=torch.int32, device=DEV)
-    _ok(lib.t2t_centroid_update(KU.to(DEV).data_ptr(), lab.to(DEV).data_ptr(), old.to(DEV).data_ptr(),
+    KUd, labd, oldd = KU.to(DEV), lab.to(DEV), old.to(DEV)      # keep the device copies alive
+    _ok(lib.t2t_centroid_update(KUd.data_ptr(), labd.data_ptr(), oldd.data_ptr(),
                                 newc.data_ptr(), counts.data_ptr(), H, N, 2048, ws.data_ptr(), ws.numel(), _st()))
+    torch.cuda.synchronize()
     assert torch.equal(counts.cpu(), want_n)
     assert torch.equal(newc.cpu().view(torch.int16), want_c.view(torch.int16))
 
@@ -158,14 +161,17 @@ def test_vstats_gather_and_gather_rows(lib, small_case):
     sumv = torch.empty(H, 2048, 128, dtype=BF, device=DEV)
     lam = torch.empty(H, dtype=torch.float32, device=DEV)
     ws = torch.empty(lib.t2t_vstats_gather_ws_bytes(H, 2048), dtype=torch.uint8, device=DEV)
-    _ok(lib.t2t_vstats_gather(v2.to(DEV).data_ptr(), kperm.to(DEV).data_ptr(), kcounts.to(DEV).data_ptr(),
+    v2d, kpermd, kcountsd, kd = v2.to(DEV), kperm.to(DEV), kcounts.to(DEV), c["k"].to(DEV)
+    _ok(lib.t2t_vstats_gather(v2d.data_ptr(), kpermd.data_ptr(), kcountsd.data_ptr(),
                               vs.data_ptr(), sumv.data_ptr(), lam.data_ptr(), H, N, 2048, ws.data_ptr(),
                               ws.numel(), _st()))
+    torch.cuda.synchronize()
     assert torch.equal(vs.cpu().view(torch.int16), want_vs.view(torch.int16))
     assert torch.equal(sumv.cpu().view(torch.int16), want_sumv.view(torch.int16))
     assert torch.equal(lam.cpu(), want_lam)
     kp = torch.empty(H, N, 128, dtype=BF, device=DEV)
-    _ok(lib.t2t_gather_rows(c["k"].to(DEV).data_ptr(), kperm.to(DEV).data_ptr(), kp.data_ptr(), H, N, _st()))
+    _ok(lib.t2t_gather_rows(kd.data_ptr(), kpermd.data_ptr(), kp.data_ptr(), H, N, _st()))
+    torch.cuda.synchronize()
     want_kp = torch.gather(c["k"], 1, kperm.long()[..., None].expand(H, N, 128))
     assert torch.equal(kp.cpu().view(torch.int16), want_kp.view(torch.int16))
 

@@ -31,6 +31,9 @@ SIGNATURES = {
     "t2t_tile_attn_plan_ints": (_S, [_I, _I, _I]),
     "t2t_tile_attn_ws_bytes": (_S, [_I, _I]),
     "t2t_tile_attn": (_I, [_P] * 15 + [_I, _I, _I, _I, _P, _S, _P, _P]),
+    "t2t_tile_attn_plan": (_I, [_P, _P, _P, _P, _I, _I, _I, _P]),
+    "t2t_tile_attn_exact": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _S, _P, _P]),
+    "t2t_tile_attn_merge": (_I, [_P] * 10 + [_I, _I, _I, _P, _S, _P, _P]),
     "t2t_tile_attn_plan_info": (_I, [_P, _I, _I, _I, _P, _P]),
     "t2t_umma_selftest": (_I, [_P, _P, _P, _P, _P, _P, _P]),
 }

@@ -130,7 +130,8 @@ __global__ void __launch_bounds__(GR_WARPS * 32) hist_kernel(const int* __restri
   const int r0 = chunk * GR_CHUNK, r1 = min(N, r0 + GR_CHUNK);
   for (int r = r0; r < r1; r += 32) {
     const int row = r + lane;
-    const int c = row < r1 ? labh[row] : -1;
+    int c = row < r1 ? labh[row] : -1;
+    if ((unsigned)c >= (unsigned)Cn) c = -1;      // a label outside [0, Cn) is ignored, never indexed
     const unsigned peers = __match_any_sync(0xffffffffu, c);
     if (c >= 0 && lane == __ffs(peers) - 1) hh[c] += __popc(peers);
     __syncwarp();
@@ -198,7 +199,8 @@ __global__ void __launch_bounds__(GR_WARPS * 32) scatter_kernel(const int* __res
   const int r0 = chunk * GR_CHUNK, r1 = min(N, r0 + GR_CHUNK);
   for (int r = r0; r < r1; r += 32) {
     const int row = r + lane;
-    const int c = row < r1 ? labh[row] : -1;
+    int c = row < r1 ? labh[row] : -1;
+    if ((unsigned)c >= (unsigned)Cn) c = -1;
     const unsigned peers = __match_any_sync(0xffffffffu, c);
     const int leader = __ffs(peers) - 1;
     const int rank = __popc(peers & ((1u << lane) - 1u));

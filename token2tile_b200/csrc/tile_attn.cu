@@ -750,42 +750,76 @@ extern "C" size_t t2t_tile_attn_ws_bytes(int H, int N) {
   return (((size_t)H * N * kD * 2 + 255) & ~(size_t)255) + (size_t)H * N * 4;
 }
 
-extern "C" int t2t_tile_attn(const void* q, const void* kp, const void* vp, const void* tile_sizes,
-                             const void* kcounts, const void* unip, const void* QU, const void* cks,
-                             const void* sumv, const void* lam, const void* qlab, const void* qperm,
-                             const float* tailw, void* out, int* plan, int rebuild_plan, int H, int N, int CQ,
-                             void* ws, size_t ws_bytes, int* d_status, cudaStream_t st) {
-  if (!q || !kp || !vp || !tile_sizes || !kcounts || !unip || !QU || !cks || !sumv || !lam || !qlab || !qperm ||
-      !tailw || !out || !plan || !ws)
-    return T2T_ERR_ARG;
-  if (H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
-  if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
-  __nv_bfloat16* attn_out = (__nv_bfloat16*)ws;
-  float* attn_lse = (float*)((char*)ws + (((size_t)H * N * kD * 2 + 255) & ~(size_t)255));
-  const PlanView pv = plan_view(plan, H, N, CQ);
+static void split_ws(void* ws, int H, int N, __nv_bfloat16** attn_out, float** attn_lse) {
+  *attn_out = (__nv_bfloat16*)ws;
+  *attn_lse = (float*)((char*)ws + (((size_t)H * N * kD * 2 + 255) & ~(size_t)255));
+}
 
-  if (rebuild_plan) {
-    if (cudaMemsetAsync(pv.counters, 0, PLAN_HDR * sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
-    kvlen_kernel<<<dim3(cdiv(CQ, 8), H), 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts,
-                                                       (const uint32_t*)unip, pv.kv_lens, CQ);
-    plan_kernel<<<H, 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts, H, N, CQ, plan);
-  } else {
-    if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
-  }
+extern "C" int t2t_tile_attn_plan(const void* tile_sizes, const void* kcounts, const void* unip, int* plan, int H,
+                                  int N, int CQ, cudaStream_t st) {
+  if (!tile_sizes || !kcounts || !unip || !plan || H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  if (cudaMemsetAsync(pv.counters, 0, PLAN_HDR * sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
+  kvlen_kernel<<<dim3(cdiv(CQ, 8), H), 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts,
+                                                     (const uint32_t*)unip, pv.kv_lens, CQ);
+  plan_kernel<<<H, 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts, H, N, CQ, plan);
+  return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}
+
+extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp, const void* unip,
+                                   const void* qperm, int* plan, int H, int N, int CQ, void* ws, size_t ws_bytes,
+                                   int* d_status, cudaStream_t st) {
+  if (!q || !kp || !vp || !unip || !qperm || !plan || !ws || H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  __nv_bfloat16* attn_out;
+  float* attn_lse;
+  split_ws(ws, H, N, &attn_out, &attn_lse);
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  // the task cursor is the only per-dispatch state of a prepared plan
+  if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
-      cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
+  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
   attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kp,
                                              (const __nv_bfloat16*)vp, (const uint32_t*)unip, (const int*)qperm,
                                              attn_out, attn_lse, plan, H, N, CQ, d_status);
+  return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}
+
+extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* sumv, const void* kcounts,
+                                   const void* unip, const void* qlab, const void* qperm, const void* lam,
+                                   const float* tailw, void* out, int H, int N, int CQ, void* ws, size_t ws_bytes,
+                                   int* d_status, cudaStream_t st) {
+  if (!QU || !cks || !sumv || !kcounts || !unip || !qlab || !qperm || !lam || !tailw || !out || !ws)
+    return T2T_ERR_ARG;
+  if (H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  __nv_bfloat16* attn_out;
+  float* attn_lse;
+  split_ws(ws, H, N, &attn_out, &attn_lse);
+  if (cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
+    return T2T_ERR_CUDA;
   tail_kernel<<<dim3(cdiv(N, TL_Q), H), 128, TL_SMEM, st>>>(
       attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const __nv_bfloat16*)sumv,
       (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
       (__nv_bfloat16*)out, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}
+
+extern "C" int t2t_tile_attn(const void* q, const void* kp, const void* vp, const void* tile_sizes,
+                             const void* kcounts, const void* unip, const void* QU, const void* cks,
+                             const void* sumv, const void* lam, const void* qlab, const void* qperm,
+                             const float* tailw, void* out, int* plan, int rebuild_plan, int H, int N, int CQ,
+                             void* ws, size_t ws_bytes, int* d_status, cudaStream_t st) {
+  int rc = T2T_OK;
+  if (rebuild_plan) rc = t2t_tile_attn_plan(tile_sizes, kcounts, unip, plan, H, N, CQ, st);
+  if (rc == T2T_OK) rc = t2t_tile_attn_exact(q, kp, vp, unip, qperm, plan, H, N, CQ, ws, ws_bytes, d_status, st);
+  if (rc == T2T_OK)
+    rc = t2t_tile_attn_merge(QU, cks, sumv, kcounts, unip, qlab, qperm, lam, tailw, out, H, N, CQ, ws, ws_bytes,
+                             d_status, st);
+  return rc;
 }
 
 extern "C" int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, int* d_info, cudaStream_t st) {

@@ -158,6 +158,10 @@ class MaskedStepDeploy:
         self.s_main = torch.cuda.Stream(device=dev)
         self.s_side = torch.cuda.Stream(device=dev)
         self.last_rebuilt = None
+        self.last_structure = None
+        # optional per-stage CUDA-event timing of step(), recorded on s_main
+        self.profile = False
+        self._marks = []
 
     def _new_structure(self):
         """Tensors that describe one structure (labels, groupings, centroids,
@@ -181,6 +185,23 @@ class MaskedStepDeploy:
                 raise ValueError(
                     f"expected contiguous bfloat16 [{self.H}, {self.N}, {self.D}] on {self.QU.device}, got "
                     f"{t.dtype} {tuple(t.shape)} on {t.device}")
+
+    # -- stage timing ------------------------------------------------------------
+    def _mark(self, name):
+        if self.profile:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record(self.s_main)
+            self._marks.append((name, ev))
+
+    def stage_times(self):
+        """Milliseconds per stage of the last step() when `profile` was set
+        (synchronises).  Stage names: project, kmeans, select, gather_k, vstats,
+        plan, attn_exact, residual_merge."""
+        torch.cuda.synchronize(self.dev)
+        out = {}
+        for (_, e0), (name, e1) in zip(self._marks[:-1], self._marks[1:]):
+            out[name] = out.get(name, 0.0) + e0.elapsed_time(e1)
+        return out
 
     # -- kernel wrappers -------------------------------------------------------
     def _project(self, x, U, out, st):
@@ -274,10 +295,13 @@ class MaskedStepDeploy:
         L = self.lib
         snap, S, publish = self._pick()
         st = _stream_ptr(self.s_main)
+        self._marks = []
         with torch.cuda.stream(self.s_main):
+            self._mark("start")
             if snap is None:
                 self._project(q, state["Uq"], self.QU, st)
                 self._project(k, state["Uk"], self.KU, st)
+                self._mark("project")
                 ck16 = torch.empty(H, C, self.r, device=self.dev, dtype=BF16)
                 check(L.t2t_kmeans_maintain(
                     ptr(self.QU), ptr(self.KU), ptr(v), ptr(state["cq"]), ptr(state["ck"]),
@@ -288,30 +312,43 @@ class MaskedStepDeploy:
                 # fresh tensors, so the next call's inputs never alias kernel outputs
                 state["ck"] = ck16
                 state["cq"] = self._kmm_cq2.clone()
+                self._mark("kmeans")
                 check(L.t2t_score_select_union(
                     ptr(self.QU), ptr(S["cks"]), ptr(S["counts"]), ptr(S["qperm"]), ptr(S["tile_sizes"]),
                     ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, st),
                     "t2t_score_select_union")
+                self._mark("select")
                 S["Uq"] = state["Uq"]
                 S["step"] = self._cfg_step
                 if publish:
                     self._cfg_hold[self._cfg_key] = S
                 check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+                self._mark("gather_k")
+                check(L.t2t_tile_attn_plan(ptr(S["tile_sizes"]), ptr(S["counts"]), ptr(S["unip"]),
+                                           ptr(S["tile_attn_plan"]), H, N, CQ, st), "t2t_tile_attn_plan")
+                self._mark("plan")
             else:
                 S = snap
                 # a reuse call projects its queries with the snapshot's Uq so that
                 # QU and the stored centroids share a basis
                 self._project(q, S["Uq"], self.QU, st)
+                self._mark("project")
                 check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+                self._mark("gather_k")
                 check(L.t2t_vstats_gather(ptr(v), ptr(S["kperm"]), ptr(S["counts"]), ptr(self.vp),
                                           ptr(self._kmm_sumv), ptr(self._kmm_lam), H, N, C, ptr(self._ws),
                                           self._ws.numel(), st), "t2t_vstats_gather")
-            check(L.t2t_tile_attn(
-                ptr(q), ptr(self.kp), ptr(self.vp), ptr(S["tile_sizes"]), ptr(S["counts"]), ptr(S["unip"]),
-                ptr(self.QU), ptr(S["cks"]), ptr(self._kmm_sumv), ptr(self._kmm_lam), ptr(S["qlab"]),
-                ptr(S["qperm"]), ptr(self.tailw_t), ptr(self.tile_attn_out), ptr(S["tile_attn_plan"]),
-                1 if snap is None else 0, H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(),
-                ptr(self.status), st), "t2t_tile_attn")
+                self._mark("vstats")
+            # the plan belongs to the structure: a reuse call only resets its task cursor
+            check(L.t2t_tile_attn_exact(
+                ptr(q), ptr(self.kp), ptr(self.vp), ptr(S["unip"]), ptr(S["qperm"]), ptr(S["tile_attn_plan"]),
+                H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_exact")
+            self._mark("attn_exact")
+            check(L.t2t_tile_attn_merge(
+                ptr(self.QU), ptr(S["cks"]), ptr(self._kmm_sumv), ptr(S["counts"]), ptr(S["unip"]),
+                ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(self.tile_attn_out),
+                H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_merge")
+            self._mark("residual_merge")
         self.last_rebuilt = snap is None
         self.last_structure = S
         # order the caller's stream after ours instead of a host sync
