@@ -247,7 +247,11 @@ def score_keys(QU16: torch.Tensor, cks16: torch.Tensor) -> torch.Tensor:
     (deploy_step.py:394; key transform select_union/src/kernel.cu:56-74,160:
     the fp16 bit pattern with its low 15 bits flipped when the sign bit is set,
     read as a signed 16-bit integer).  One head: QU16 [n, r], cks16 [C, r]."""
-    g = chain_dot(QU16.to(F32), cks16.to(F32)).to(torch.float16)
+    return keys_from_fp16(chain_dot(QU16.to(F32), cks16.to(F32)).to(torch.float16))
+
+
+def keys_from_fp16(g: torch.Tensor) -> torch.Tensor:
+    """Order-preserving signed 16-bit key of an fp16 score (kernel.cu:56-74, 160)."""
     u = g.view(torch.int16).to(torch.int32) & 0xFFFF
     u = u ^ (((u >> 15) & 1) * 0x7FFF)
     return ((u ^ 0x8000) - 0x8000).to(torch.int16)
@@ -287,18 +291,21 @@ def unpack_bits(words: torch.Tensor, C: int) -> torch.Tensor:
 
 
 def select_union(QU16, cks16, kcounts, qlab, CQ: int, ns: int, pin_tail: int = 0,
-                 row_chunk: int = 2048):
+                 row_chunk: int = 2048, gl16=None):
     """Union bitmap unip [H, CQ, C/32] int32 and rowcnt [H, N] int32.
     U_t = OR of the selections of the queries labelled t; pin_tail > 0 also
-    sets cluster C-1 everywhere (deploy_step.py:444-448)."""
-    H, N, _ = QU16.shape
-    C = cks16.shape[1]
+    sets cluster C-1 everywhere (deploy_step.py:444-448).  With gl16 (an fp16
+    score matrix [H, N, C], the reference's `gl`) the scores are taken from it
+    instead of being recomputed."""
+    H, N = qlab.shape
+    C = kcounts.shape[1]
     hits = torch.zeros(H, CQ, C, dtype=torch.int32)
     rowcnt = torch.empty(H, N, dtype=torch.int32)
     for h in range(H):
         lab = qlab[h].to(torch.int64)
         for s in range(0, N, row_chunk):
-            keys = score_keys(QU16[h, s:s + row_chunk], cks16[h])
+            keys = (score_keys(QU16[h, s:s + row_chunk], cks16[h]) if gl16 is None
+                    else keys_from_fp16(gl16[h, s:s + row_chunk]))
             sel, rc = select_rows(keys, kcounts[h], ns)
             rowcnt[h, s:s + row_chunk] = rc
             hits[h].index_add_(0, lab[s:s + row_chunk], sel.to(torch.int32))

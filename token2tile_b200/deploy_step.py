@@ -25,8 +25,14 @@ import math
 
 import torch
 
-from . import _lib
-from ._lib import check, ptr
+try:
+    from . import _lib
+except ImportError:      # imported as a top-level module from operator_dir(), the way the reference's hosts do
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from token2tile_b200 import _lib
+check, ptr = _lib.check, _lib.ptr
 
 BF16 = torch.bfloat16
 
