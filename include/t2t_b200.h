@@ -28,6 +28,7 @@ enum {
   T2T_ERR_ARG = 1,        /* null pointer, non-positive size, unsupported shape */
   T2T_ERR_CUDA = 2,       /* a launch or attribute call failed */
   T2T_ERR_WORKSPACE = 3,  /* workspace too small */
+  T2T_ERR_TOO_LARGE = 4,  /* shape exceeds the fixed capacity of a no-allocation entry point */
 };
 enum {
   T2T_ST_OK = 0,
@@ -87,6 +88,28 @@ int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const voi
 size_t t2t_vstats_gather_ws_bytes(int H, int C);
 int t2t_vstats_gather(const void* V, const void* kperm, const void* kcounts, void* V_sorted, void* sumv,
                       void* lam, int H, int N, int C, void* ws, size_t ws_bytes, cudaStream_t stream);
+
+/* t2t_vstats_gather for callers that cannot allocate device memory.  It has no
+ * counterpart in the reference.  Some hosts hand the whole device to their own
+ * memory pool when they start (serving engines that pre-size their caches), or
+ * run under a policy that forbids driver allocations on the request path
+ * because cudaMalloc can fail late or stall the device; such a caller has no
+ * workspace to pass.  This variant takes none: its scratch is a fixed array
+ * inside the library image, T2T_STATIC_VSTATS_MAX_HC * 516 bytes (about 4 MB)
+ * resident on every GPU that loads the library, for as long as the process
+ * lives.  Inputs and outputs are still the caller's.  Limits and rules:
+ *   - H * C must not exceed T2T_STATIC_VSTATS_MAX_HC (4 heads of 2048
+ *     clusters); larger shapes return T2T_ERR_TOO_LARGE and launch nothing;
+ *   - the first call on each device looks up the array's device address (with
+ *     that device current); make that first call outside any stream capture;
+ *   - all calls share the one array and it keeps the last call's contents; the
+ *     kernels overwrite every word before reading it, so nothing is cleared,
+ *     but two calls that overlap on the GPU (different streams) race;
+ *   - it calls no cudaMalloc, cudaFree or allocating library routine. */
+#define T2T_STATIC_VSTATS_MAX_HC 8192
+size_t t2t_vstats_gather_static_max_hc(void);
+int t2t_vstats_gather_static(const void* V, const void* kperm, const void* kcounts, void* V_sorted, void* sumv,
+                             void* lam, int H, int N, int C, cudaStream_t stream);
 
 /* out[h,i,:] = x[h,perm[h,i],:] for rows of 128 bf16.  Replaces
  * fast_gather(x, perm, out), fast_permute.py:54-56. */

@@ -11,7 +11,8 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "libt2t_b200.so"
 _lib = None
 
-ERRORS = {1: "bad argument", 2: "CUDA launch failed", 3: "workspace too small"}
+ERRORS = {1: "bad argument", 2: "CUDA launch failed", 3: "workspace too small",
+          4: "shape exceeds the fixed capacity of a no-allocation entry point"}
 STATUS = {0: "ok", 1: "a bounded device wait timed out", 2: "task plan exceeded its bounds"}
 
 _P, _I, _S, _F = C.c_void_p, C.c_int, C.c_size_t, C.c_float
@@ -26,6 +27,8 @@ SIGNATURES = {
     "t2t_kmeans_maintain": (_I, [_P] * 18 + [_F, _I, _I, _I, _I, _I, _P, _S, _P]),
     "t2t_vstats_gather_ws_bytes": (_S, [_I, _I]),
     "t2t_vstats_gather": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _S, _P]),
+    "t2t_vstats_gather_static_max_hc": (_S, []),
+    "t2t_vstats_gather_static": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "t2t_gather_rows": (_I, [_P, _P, _P, _I, _I, _P]),
     "t2t_score_select_union": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "t2t_tile_attn_plan_ints": (_S, [_I, _I, _I]),

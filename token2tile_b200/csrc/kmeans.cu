@@ -558,3 +558,46 @@ extern "C" int t2t_gather_rows(const void* x, const void* perm, void* out, int H
                                                                      (uint4*)out, N, total);
   return finish();
 }
+
+// ---------------------------------------------------------------------------
+// value statistics without any allocation
+// ---------------------------------------------------------------------------
+// Scratch for t2t_vstats_gather_static.  It is part of the library image: every
+// GPU that loads the library holds these bytes until the process exits.
+namespace t2t {
+constexpr int kStaticMaxHeads = T2T_STATIC_VSTATS_MAX_HC / kC;
+constexpr size_t kStaticScratchBytes =
+    (((size_t)T2T_STATIC_VSTATS_MAX_HC * sizeof(int) + 255) & ~(size_t)255) +
+    (((size_t)T2T_STATIC_VSTATS_MAX_HC * kD * sizeof(float) + 255) & ~(size_t)255) +
+    (((size_t)kStaticMaxHeads * VM_BLOCKS * sizeof(float) + 255) & ~(size_t)255);
+static __device__ __align__(256) unsigned char g_vstats_scratch[kStaticScratchBytes];
+constexpr int kMaxDevices = 64;
+static void* g_vstats_scratch_addr[kMaxDevices];   // device address of the array, per device
+}  // namespace t2t
+
+extern "C" size_t t2t_vstats_gather_static_max_hc(void) { return T2T_STATIC_VSTATS_MAX_HC; }
+
+extern "C" int t2t_vstats_gather_static(const void* V, const void* kperm, const void* kcounts, void* V_sorted,
+                                        void* sumv, void* lam, int H, int N, int C, cudaStream_t st) {
+  if (!V || !kperm || !kcounts || !V_sorted || !sumv || !lam || H <= 0 || N <= 0 || C <= 0) return T2T_ERR_ARG;
+  if ((size_t)H * (size_t)C > (size_t)T2T_STATIC_VSTATS_MAX_HC) return T2T_ERR_TOO_LARGE;
+  VstatWs probe = vstat_layout(H, C, nullptr);
+  if (probe.total > kStaticScratchBytes) return T2T_ERR_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return T2T_ERR_CUDA;
+  if (!g_vstats_scratch_addr[dev]) {
+    // In host code the array's name is only a handle; the kernels need the
+    // address it has on the current device.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_vstats_scratch) != cudaSuccess || !p) return T2T_ERR_CUDA;
+    g_vstats_scratch_addr[dev] = p;
+  }
+  VstatWs w = vstat_layout(H, C, g_vstats_scratch_addr[dev]);
+  // Every word of the scratch that is read is written first in the same call
+  // (bases, sums and block maxima cover all H * C clusters), so nothing has to
+  // be cleared although the array keeps the previous call's contents.
+  bases_kernel<<<H, 1024, 0, st>>>((const int*)kcounts, w.cbase, C);
+  launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase, (bf16*)V_sorted, (bf16*)sumv,
+                (float*)lam, w.vsum, w.bmax, H, N, C, st);
+  return finish();
+}
