@@ -184,7 +184,13 @@ def run_ours(args, rank, world, local_rank):
     from token2tile_b200.synth import GRIDS, locality_mixture
     import torch.distributed as dist
 
-    W = WORKLOAD
+    W = dict(WORKLOAD)
+    if args.heads or args.grid:      # smaller cases for profiler captures; the default is the 720p layer
+        W["H"] = args.heads or W["H"]
+        W["grid"] = args.grid or W["grid"]
+        W["N"] = GRIDS[W["grid"]][0] * GRIDS[W["grid"]][1] * GRIDS[W["grid"]][2]
+        W["CQ"] = {"720p": 512, "480p": 256, "cpu": 32}[W["grid"]]
+        W["name"] = f"self-attention-layer-{W['grid']}-{W['H']}heads"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     if world > 1:
@@ -233,6 +239,14 @@ def run_ours(args, rank, world, local_rank):
     stages = op.stage_times()
     op.profile = False
     tasks, pairs = op.plan_info()
+    if args.light:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world,
+                              "config": {"workload": W["name"], "H": W["H"], "N": N, "CQ": CQ},
+                              "stages_ms": stages, "tasks": tasks, "pairs": pairs, "clocks": clocks}))
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # end to end: host buffers in, host buffer out, through the same call
     def e2e_step():
@@ -338,6 +352,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--heads", type=int, default=0, help="override the head count (profiling cases)")
+    ap.add_argument("--grid", default="", choices=["", "cpu", "480p", "720p"], help="override the latent grid")
+    ap.add_argument("--light", action="store_true", help="timed steps and stage times only")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
