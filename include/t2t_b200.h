@@ -48,12 +48,20 @@ int t2t_project(const void* x, const void* U, void* out, int H, int N, int* d_st
 
 /* labels[h,i] = argmin_c(||c||^2 - 2 x_i.c), ties to the lowest c; rows >=
  * pin_begin get pin_label when pin_begin >= 0.  x bf16 [H,N,32], cen bf16
- * [H,Cn,32], labels int32 [H,N].  The distance is the fp32 fused-multiply-add
- * chain over k = 0..31 started at ||c||^2, so labels are reproducible bit for
- * bit on any machine.  Replaces fast_assign(x, centroids), fast_assign.py:79-106
- * and assign_kernel, kernels/kmeans_maintain/src/kernels.cu:104-257. */
+ * [H,Cn,32], labels int32 [H,N].  The distance is DEFINED as the fp32
+ * fused-multiply-add chain over k = 0..31 started at ||c||^2, so labels are
+ * reproducible bit for bit on any machine.  t2t_assign finds them with a
+ * tcgen05 product and re-evaluates by the exact chain only the rows whose two
+ * nearest centroids are closer than the product's error bound;
+ * t2t_assign_exact evaluates the chain for every pair (slow; the cross-check).
+ * Both give identical labels.  ws: t2t_assign_ws_bytes(H, N).  Replaces
+ * fast_assign(x, centroids), fast_assign.py:79-106 and assign_kernel,
+ * kernels/kmeans_maintain/src/kernels.cu:104-257. */
+size_t t2t_assign_ws_bytes(int H, int N);
 int t2t_assign(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
-               int pin_label, cudaStream_t stream);
+               int pin_label, void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
+int t2t_assign_exact(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
+                     int pin_label, cudaStream_t stream);
 
 /* Deterministic centroid update from labels: integer fixed-point (2^15) sums,
  * newc = bf16(float(sum) / (2^15 n)), an empty cluster keeps `old`.  x bf16
@@ -80,7 +88,7 @@ int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const voi
                         void* qlab, void* cq2, void* klab, void* ck2, void* ck16, void* cks16,
                         void* qcounts, void* qperm, void* kcounts, void* kperm, void* V_sorted,
                         void* sumv, void* lam, float scale, int H, int N, int CQ, int C, int pin_tail,
-                        void* ws, size_t ws_bytes, cudaStream_t stream);
+                        void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
 
 /* Reuse call: V_sorted = V[kperm], value sums and lam from this call's V with
  * the stored grouping.  Replaces reuse_vstats_gather_launch,

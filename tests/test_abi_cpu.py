@@ -34,7 +34,8 @@ def test_workspace_sizes_are_pure_host_functions(lib):
 
 def test_null_and_bad_arguments_are_rejected(lib):
     assert lib.t2t_project(0, 0, 0, 1, 1, 0, 0) == 1
-    assert lib.t2t_assign(0, 0, 0, 2, 4096, 32, -1, 0, 0) == 1
+    assert lib.t2t_assign(0, 0, 0, 2, 4096, 32, -1, 0, 0, 0, 0, 0) == 1
+    assert lib.t2t_assign_exact(0, 0, 0, 2, 4096, 32, -1, 0, 0) == 1
     assert lib.t2t_gather_rows(0, 0, 0, 2, 4096, 0) == 1
     assert lib.t2t_vstats_gather(0, 0, 0, 0, 0, 0, 2, 4096, 2048, 0, 0, 0) == 1
     assert lib.t2t_tile_attn_plan(0, 0, 0, 0, 2, 4096, 32, 0) == 1

@@ -39,6 +39,13 @@ def test_umma_selftest(lib):
     assert int(status.item()) == 0
     S_ref = A.float() @ B.float().T
     assert torch.allclose(S.cpu(), S_ref, atol=1e-3, rtol=1e-4), (S.cpu() - S_ref).abs().max()
+    # accumulation error of the tensor core against the real sum, relative to sum |a||b|: the assignment
+    # and selection kernels assume it is below 2^-16
+    S64 = A.double() @ B.double().T
+    mag = A.double().abs() @ B.double().abs().T
+    kappa = float(((S.cpu().double() - S64).abs() / mag).max())
+    print(f"tensor-core accumulation error: {kappa:.3e} of sum|a||b| (2^{math.log2(kappa):.1f})")
+    assert kappa < 2.0 ** -18
     P = (S.cpu() * 0.0625).to(BF).float()
     O_ref = P @ V.float()
     assert torch.allclose(Oo.cpu(), O_ref, atol=2e-3, rtol=1e-4), (Oo.cpu() - O_ref).abs().max()
@@ -61,11 +68,37 @@ def test_project(lib, small_case):
 
 
 def _assign(lib, x, cen, pin_begin=-1, pin_label=0):
+    """Tensor-core assignment; also checks it against the all-exact kernel."""
     H, N, _ = x.shape
     lab = torch.empty(H, N, dtype=torch.int32, device=DEV)
-    _ok(lib.t2t_assign(x.data_ptr(), cen.data_ptr(), lab.data_ptr(), H, N, cen.shape[1], pin_begin, pin_label, _st()))
+    lab_exact = torch.empty_like(lab)
+    ws = torch.empty(lib.t2t_assign_ws_bytes(H, N), dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _ok(lib.t2t_assign(x.data_ptr(), cen.data_ptr(), lab.data_ptr(), H, N, cen.shape[1], pin_begin, pin_label,
+                       ws.data_ptr(), ws.numel(), status.data_ptr(), _st()))
+    _ok(lib.t2t_assign_exact(x.data_ptr(), cen.data_ptr(), lab_exact.data_ptr(), H, N, cen.shape[1], pin_begin,
+                             pin_label, _st()))
     torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert torch.equal(lab, lab_exact)
+    _assign.requeued = int(ws[:4].view(torch.int32).item())
     return lab
+
+
+def test_assign_tensor_core_path_equals_exact_path_at_scale(lib):
+    """480p-sized random problem: the tensor-core labels must equal the all-exact
+    labels, with only a small share of rows sent to the exact re-evaluation."""
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    H, N = 4, 32760
+    q, k, _ = locality_mixture(H, GRIDS["480p"])
+    g = torch.Generator().manual_seed(5)
+    U = (torch.randn(H, 128, 32, generator=g) * 0.1).to(BF)
+    x = torch.bmm(k.float(), U.float()).to(BF).to(DEV)
+    for Cn in (2048, 256):
+        idx = torch.randperm(N, generator=g)[:Cn].sort().values
+        cen = x[:, idx.to(DEV), :].contiguous()
+        _assign(lib, x, cen)
+        assert _assign.requeued < 0.05 * H * N, _assign.requeued
 
 
 def test_assign_bit_exact(lib, small_case):
@@ -125,7 +158,7 @@ def _kmm(lib, QU, KU, V, cq0, ck0, CQ, pin_tail=0):
     order = ["qlab", "cq2", "klab", "ck2", "ck16", "cks16", "qcounts", "qperm", "kcounts", "kperm", "V_sorted",
              "sumv", "lam"]
     _ok(lib.t2t_kmeans_maintain(*[t.data_ptr() for t in dev], *[out[k].data_ptr() for k in order],
-                                1.0 / math.sqrt(128.0), H, N, CQ, C, pin_tail, ws.data_ptr(), ws.numel(), _st()))
+                                1.0 / math.sqrt(128.0), H, N, CQ, C, pin_tail, ws.data_ptr(), ws.numel(), 0, _st()))
     torch.cuda.synchronize()
     return {k: t.cpu() for k, t in out.items()}
 

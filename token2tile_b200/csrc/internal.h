@@ -1,0 +1,18 @@
+// Launchers shared between translation units of libt2t_b200.so (not part of the C ABI).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+#include "t2t_b200.h"
+
+namespace t2t {
+
+// Tensor-core assignment with exact verification (assign_tc.cu).  `amb` is a
+// scratch list of (H * N + 1) ints: a counter followed by the rows queued for
+// the exact re-evaluation.
+size_t assign_ws_bytes(int H, int N);
+int launch_assign(const __nv_bfloat16* X, const __nv_bfloat16* cen, int* labels, int H, int N, int Cn,
+                  int pin_begin, int pin_label, int* amb, int* d_status, cudaStream_t st);
+
+}  // namespace t2t

@@ -10,19 +10,19 @@
 // fixed order, sums are either integers or accumulated in grouped row order by
 // one owner warp.
 #include "common.cuh"
-#include "t2t_b200.h"
+#include "internal.h"
 
 namespace t2t {
 
 // ---------------------------------------------------------------------------
-// assignment
+// assignment, all-exact form (the definition the tensor-core path must reproduce)
 // ---------------------------------------------------------------------------
 constexpr int AS_THREADS = 256;
 constexpr int AS_RPT = 2;                       // rows per thread
 constexpr int AS_ROWS = AS_THREADS * AS_RPT;    // rows per CTA
 constexpr int AS_CT = 128;                      // centroids staged per step
 
-__global__ void __launch_bounds__(AS_THREADS) assign_kernel(const __nv_bfloat16* __restrict__ X,
+__global__ void __launch_bounds__(AS_THREADS) assign_exact_kernel(const __nv_bfloat16* __restrict__ X,
                                                             const __nv_bfloat16* __restrict__ cen,
                                                             int* __restrict__ labels, int N, int Cn,
                                                             int pin_begin, int pin_label) {
@@ -412,7 +412,7 @@ struct Carver {
 };
 
 struct KmmWs {
-  int *qlab1, *chist, *cbase_q, *cbase_k;
+  int *qlab1, *chist, *cbase_q, *cbase_k, *amb;
   __nv_bfloat16* cq1;
   float *vsum, *bmax;
   size_t total;
@@ -422,6 +422,7 @@ static KmmWs kmm_layout(int H, int N, int CQ, int C, void* base) {
   KmmWs w;
   const int nChunk = cdiv(N, GR_CHUNK);
   w.qlab1 = cv.take<int>((size_t)H * N);
+  w.amb = cv.take<int>((size_t)H * N + 1);
   w.chist = cv.take<int>((size_t)H * nChunk * (C > CQ ? C : CQ));
   w.cbase_q = cv.take<int>((size_t)H * CQ);
   w.cbase_k = cv.take<int>((size_t)H * C);
@@ -474,12 +475,22 @@ typedef __nv_bfloat16 bf16;
 
 extern "C" int t2t_version(void) { return 100; }
 
-extern "C" int t2t_assign(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
-                          int pin_label, cudaStream_t st) {
+extern "C" int t2t_assign_exact(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
+                                int pin_label, cudaStream_t st) {
   if (!x || !cen || !labels || H <= 0 || N <= 0 || Cn <= 0) return T2T_ERR_ARG;
-  assign_kernel<<<dim3(cdiv(N, AS_ROWS), H), AS_THREADS, 0, st>>>((const bf16*)x, (const bf16*)cen, (int*)labels,
-                                                                  N, Cn, pin_begin, pin_label);
+  assign_exact_kernel<<<dim3(cdiv(N, AS_ROWS), H), AS_THREADS, 0, st>>>((const bf16*)x, (const bf16*)cen,
+                                                                        (int*)labels, N, Cn, pin_begin, pin_label);
   return finish();
+}
+
+extern "C" size_t t2t_assign_ws_bytes(int H, int N) { return assign_ws_bytes(H, N); }
+
+extern "C" int t2t_assign(const void* x, const void* cen, void* labels, int H, int N, int Cn, int pin_begin,
+                          int pin_label, void* ws, size_t ws_bytes, int* d_status, cudaStream_t st) {
+  if (!x || !cen || !labels || !ws || H <= 0 || N <= 0 || Cn <= 0) return T2T_ERR_ARG;
+  if (ws_bytes < assign_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  return launch_assign((const bf16*)x, (const bf16*)cen, (int*)labels, H, N, Cn, pin_begin, pin_label, (int*)ws,
+                       d_status, st);
 }
 
 extern "C" size_t t2t_centroid_update_ws_bytes(int H, int N, int Cn) { return upd_layout(H, N, Cn, nullptr).total; }
@@ -504,7 +515,8 @@ extern "C" int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V
                                    const void* ck0, void* qlab, void* cq2, void* klab, void* ck2, void* ck16,
                                    void* cks16, void* qcounts, void* qperm, void* kcounts, void* kperm,
                                    void* V_sorted, void* sumv, void* lam, float scale, int H, int N, int CQ,
-                                   int C, int pin_tail, void* ws, size_t ws_bytes, cudaStream_t st) {
+                                   int C, int pin_tail, void* ws, size_t ws_bytes, int* d_status,
+                                   cudaStream_t st) {
   if (!QU || !KU || !V || !cq0 || !ck0 || !qlab || !cq2 || !klab || !ck2 || !ck16 || !cks16 || !qcounts ||
       !qperm || !kcounts || !kperm || !V_sorted || !sumv || !lam || !ws)
     return T2T_ERR_ARG;
@@ -512,21 +524,24 @@ extern "C" int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V
     return T2T_ERR_ARG;
   KmmWs w = kmm_layout(H, N, CQ, C, ws);
   if (ws_bytes < w.total) return T2T_ERR_WORKSPACE;
-  const dim3 agrid(cdiv(N, AS_ROWS), H);
+  int rc;
   const dim3 qgrid(cdiv(CQ, CS_WARPS), H), kgrid(cdiv(C, CS_WARPS), H);
   // queries, pass 1
-  assign_kernel<<<agrid, AS_THREADS, 0, st>>>((const bf16*)QU, (const bf16*)cq0, w.qlab1, N, CQ, -1, 0);
+  rc = launch_assign((const bf16*)QU, (const bf16*)cq0, w.qlab1, H, N, CQ, -1, 0, w.amb, d_status, st);
+  if (rc != T2T_OK) return rc;
   launch_group(w.qlab1, w.chist, (int*)qcounts, w.cbase_q, (int*)qperm, H, N, CQ, st);
   fixed_mean_kernel<<<qgrid, CS_WARPS * 32, 0, st>>>((const bf16*)QU, (const int*)qperm, (const int*)qcounts,
                                                     w.cbase_q, (const bf16*)cq0, w.cq1, N, CQ);
   // queries, pass 2
-  assign_kernel<<<agrid, AS_THREADS, 0, st>>>((const bf16*)QU, w.cq1, (int*)qlab, N, CQ, -1, 0);
+  rc = launch_assign((const bf16*)QU, w.cq1, (int*)qlab, H, N, CQ, -1, 0, w.amb, d_status, st);
+  if (rc != T2T_OK) return rc;
   launch_group((const int*)qlab, w.chist, (int*)qcounts, w.cbase_q, (int*)qperm, H, N, CQ, st);
   fixed_mean_kernel<<<qgrid, CS_WARPS * 32, 0, st>>>((const bf16*)QU, (const int*)qperm, (const int*)qcounts,
                                                     w.cbase_q, w.cq1, (bf16*)cq2, N, CQ);
   // keys
-  assign_kernel<<<agrid, AS_THREADS, 0, st>>>((const bf16*)KU, (const bf16*)ck0, (int*)klab, N, C,
-                                              pin_tail > 0 ? N - pin_tail : -1, C - 1);
+  rc = launch_assign((const bf16*)KU, (const bf16*)ck0, (int*)klab, H, N, C, pin_tail > 0 ? N - pin_tail : -1,
+                     C - 1, w.amb, d_status, st);
+  if (rc != T2T_OK) return rc;
   launch_group((const int*)klab, w.chist, (int*)kcounts, w.cbase_k, (int*)kperm, H, N, C, st);
   key_mean_kernel<<<kgrid, CS_WARPS * 32, 0, st>>>((const bf16*)KU, (const int*)kperm, (const int*)kcounts,
                                                   w.cbase_k, (const bf16*)ck0, (float*)ck2, (bf16*)ck16,

@@ -145,7 +145,7 @@ class MaskedStepDeploy:
         self._tile_attn_plan_ints = int(L.t2t_tile_attn_plan_ints(H, N, CQ))
         ws = max(int(L.t2t_kmeans_maintain_ws_bytes(H, N, CQ, C)),
                  int(L.t2t_vstats_gather_ws_bytes(H, C)),
-                 int(L.t2t_centroid_update_ws_bytes(H, N, C)))
+                 int(L.t2t_centroid_update_ws_bytes(H, N, C)), int(L.t2t_assign_ws_bytes(H, N)))
         self._ws = e(ws, dtype=torch.uint8)
         self._attn_ws = e(int(L.t2t_tile_attn_ws_bytes(H, N)), dtype=torch.uint8)
         self._struct = self._new_structure()      # structure of unannotated calls
@@ -214,8 +214,8 @@ class MaskedStepDeploy:
         check(self.lib.t2t_project(ptr(x), ptr(U), ptr(out), self.H, self.N, ptr(self.status), st), "t2t_project")
 
     def _assign(self, x, cen, labels, st):
-        check(self.lib.t2t_assign(ptr(x), ptr(cen), ptr(labels), self.H, self.N, cen.shape[1], -1, 0, st),
-              "t2t_assign")
+        check(self.lib.t2t_assign(ptr(x), ptr(cen), ptr(labels), self.H, self.N, cen.shape[1], -1, 0,
+                                  ptr(self._ws), self._ws.numel(), ptr(self.status), st), "t2t_assign")
 
     def _centroid_update(self, x, labels, old, st):
         newc = torch.empty_like(old)
@@ -314,7 +314,7 @@ class MaskedStepDeploy:
                     ptr(S["qlab"]), ptr(self._kmm_cq2), ptr(S["klab"]), ptr(self._kmm_ck2), ptr(ck16),
                     ptr(S["cks"]), ptr(S["tile_sizes"]), ptr(S["qperm"]), ptr(S["counts"]), ptr(S["kperm"]),
                     ptr(self.vp), ptr(self._kmm_sumv), ptr(self._kmm_lam), self.scale, H, N, CQ, C,
-                    self.pin_tail, ptr(self._ws), self._ws.numel(), st), "t2t_kmeans_maintain")
+                    self.pin_tail, ptr(self._ws), self._ws.numel(), ptr(self.status), st), "t2t_kmeans_maintain")
                 # fresh tensors, so the next call's inputs never alias kernel outputs
                 state["ck"] = ck16
                 state["cq"] = self._kmm_cq2.clone()
