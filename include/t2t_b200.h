@@ -123,20 +123,30 @@ int t2t_vstats_gather_static(const void* V, const void* kperm, const void* kcoun
  * fast_gather(x, perm, out), fast_permute.py:54-56. */
 int t2t_gather_rows(const void* x, const void* perm, void* out, int H, int N, cudaStream_t stream);
 
-/* Scoring and selection fused: g = fp16(QU_i . cks_c) (fp32 chain), clusters
- * ordered by (g descending, index ascending), a cluster is selected iff the
- * sizes before it sum to < *ns; the selections of a query cluster are OR-ed
- * into unip int32 [H,CQ,64] (bit b of word w = cluster 32 w + b); rowcnt int32
- * [H,N] is the selected token count per query.  qperm/tile_sizes are the query
- * grouping; ns is a device int32 read by the kernel; pin_tail > 0 also sets
- * cluster C-1 in every row.  The [H,N,2048] score matrix is never stored.
- * Replaces torch.bmm(QU, cks^T, out=gl), deploy_step.py:394, and
- * fscu_packed_launch / fscu_split_packed_launch,
- * kernels/select_union/src/kernel.h:19-29 (kernel.cu:523-556), and the
- * pin_tail OR at deploy_step.py:444-448. */
+/* Scoring and selection fused: g = fp16(QU_i . cks_c) (DEFINED as the fp32
+ * fused-multiply-add chain over k), clusters ordered by (g descending, index
+ * ascending), a cluster is selected iff the sizes before it sum to < *ns; the
+ * selections of a query cluster are OR-ed into unip int32 [H,CQ,64] (bit b of
+ * word w = cluster 32 w + b); rowcnt int32 [H,N] is the selected token count per
+ * query.  qperm/tile_sizes are the query grouping; ns is a device int32 read by
+ * the kernel (N < 2^19); pin_tail > 0 also sets cluster C-1 in every row.  The
+ * [H,N,2048] score matrix is never stored.  t2t_score_select_union scores on
+ * the tensor cores and settles each row from the approximate scores plus exact
+ * chain scores of the few clusters near its threshold; rows it cannot settle
+ * that way go to the exact routine.  t2t_score_select_union_exact evaluates
+ * every chain (slow; the cross-check).  Both give identical results.  ws:
+ * t2t_score_select_union_ws_bytes(H, N).  Replaces torch.bmm(QU, cks^T, out=gl),
+ * deploy_step.py:394, fscu_packed_launch / fscu_split_packed_launch,
+ * kernels/select_union/src/kernel.h:19-29 (kernel.cu:523-556), and the pin_tail
+ * OR at deploy_step.py:444-448. */
+size_t t2t_score_select_union_ws_bytes(int H, int N);
 int t2t_score_select_union(const void* QU, const void* cks, const void* kcounts, const void* qperm,
                            const void* tile_sizes, const int* ns, void* unip, void* rowcnt, int H,
-                           int N, int CQ, int pin_tail, cudaStream_t stream);
+                           int N, int CQ, int pin_tail, void* ws, size_t ws_bytes, int* d_status,
+                           cudaStream_t stream);
+int t2t_score_select_union_exact(const void* QU, const void* cks, const void* kcounts, const void* qperm,
+                                 const void* tile_sizes, const int* ns, void* unip, void* rowcnt, int H,
+                                 int N, int CQ, int pin_tail, cudaStream_t stream);
 
 /* Task plan + exact attention over the unions + centroid residual + merge.
  * q bf16 [H,N,128] original order; kp/vp bf16 [H,N,128] cluster-major;

@@ -37,6 +37,8 @@ def test_null_and_bad_arguments_are_rejected(lib):
     assert lib.t2t_assign(0, 0, 0, 2, 4096, 32, -1, 0, 0, 0, 0, 0) == 1
     assert lib.t2t_assign_exact(0, 0, 0, 2, 4096, 32, -1, 0, 0) == 1
     assert lib.t2t_gather_rows(0, 0, 0, 2, 4096, 0) == 1
+    assert lib.t2t_score_select_union(0, 0, 0, 0, 0, 0, 0, 0, 2, 4096, 32, 0, 0, 0, 0, 0) == 1
+    assert lib.t2t_score_select_union_exact(0, 0, 0, 0, 0, 0, 0, 0, 2, 4096, 32, 0, 0) == 1
     assert lib.t2t_vstats_gather(0, 0, 0, 0, 0, 0, 2, 4096, 2048, 0, 0, 0) == 1
     assert lib.t2t_tile_attn_plan(0, 0, 0, 0, 2, 4096, 32, 0) == 1
     assert lib.t2t_umma_selftest(0, 0, 0, 0, 0, 0, 0) == 1

@@ -213,13 +213,43 @@ def _select(lib, QU, cks, kcounts, qperm, qcounts, ns, pin_tail=0):
     H, N, _ = QU.shape
     CQ = qcounts.shape[1]
     unip = torch.empty(H, CQ, 64, dtype=torch.int32, device=DEV)
-    rowcnt = torch.empty(H, N, dtype=torch.int32, device=DEV)
+    rowcnt = torch.full((H, N), -7, dtype=torch.int32, device=DEV)
+    unip_x, rowcnt_x = torch.empty_like(unip), torch.empty_like(rowcnt)
     ns_t = torch.tensor(ns, dtype=torch.int32, device=DEV)
+    ws = torch.empty(lib.t2t_score_select_union_ws_bytes(H, N), dtype=torch.uint8, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
     dev = [t.to(DEV) for t in (QU, cks, kcounts, qperm, qcounts)]
     _ok(lib.t2t_score_select_union(*[t.data_ptr() for t in dev], ns_t.data_ptr(), unip.data_ptr(),
-                                   rowcnt.data_ptr(), H, N, CQ, pin_tail, _st()))
+                                   rowcnt.data_ptr(), H, N, CQ, pin_tail, ws.data_ptr(), ws.numel(),
+                                   status.data_ptr(), _st()))
+    _ok(lib.t2t_score_select_union_exact(*[t.data_ptr() for t in dev], ns_t.data_ptr(), unip_x.data_ptr(),
+                                         rowcnt_x.data_ptr(), H, N, CQ, pin_tail, _st()))
     torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    # the tensor-core path and the all-exact path must agree bit for bit
+    assert torch.equal(rowcnt, rowcnt_x)
+    assert torch.equal(unip, unip_x)
+    q = ws.view(torch.int32).view(H, 2 * N + 1)[:, 0]
+    _select.requeued = int(q.sum().item())
     return unip.cpu(), rowcnt.cpu()
+
+
+def test_select_tensor_core_path_equals_exact_path_at_scale(lib):
+    """480p-sized problem through real clustering: both selection paths must agree
+    and only a small share of rows may need the exact re-evaluation."""
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    H, N, CQ = 2, 32760, 256
+    q, k, v = locality_mixture(H, GRIDS["480p"])
+    g = torch.Generator().manual_seed(9)
+    Uq = (torch.randn(H, 128, 32, generator=g) * 0.1).to(BF)
+    QU = torch.bmm(q.float(), Uq.float()).to(BF)
+    KU = torch.bmm(k.float(), Uq.float()).to(BF)
+    ck0 = KU[:, torch.randperm(N, generator=g)[:2048].sort().values].contiguous()
+    cq0 = QU[:, torch.randperm(N, generator=g)[:CQ].sort().values].contiguous()
+    km = _kmm(lib, QU, KU, v, cq0, ck0, CQ)
+    for ns in (491, 1638, 5):
+        _select(lib, QU, km["cks16"], km["kcounts"], km["qperm"], km["qcounts"], ns)
+        assert _select.requeued < 0.02 * H * N, (ns, _select.requeued)
 
 
 @pytest.mark.parametrize("ns,pin_tail", [(204, 0), (1, 0), (4096, 0), (61, 33)])

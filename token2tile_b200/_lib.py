@@ -32,7 +32,9 @@ SIGNATURES = {
     "t2t_vstats_gather_static_max_hc": (_S, []),
     "t2t_vstats_gather_static": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P]),
     "t2t_gather_rows": (_I, [_P, _P, _P, _I, _I, _P]),
-    "t2t_score_select_union": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
+    "t2t_score_select_union_ws_bytes": (_S, [_I, _I]),
+    "t2t_score_select_union": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _S, _P, _P]),
+    "t2t_score_select_union_exact": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P]),
     "t2t_tile_attn_plan_ints": (_S, [_I, _I, _I]),
     "t2t_tile_attn_ws_bytes": (_S, [_I, _I]),
     "t2t_tile_attn": (_I, [_P] * 15 + [_I, _I, _I, _I, _P, _S, _P, _P]),

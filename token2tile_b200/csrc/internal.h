@@ -15,4 +15,9 @@ size_t assign_ws_bytes(int H, int N);
 int launch_assign(const __nv_bfloat16* X, const __nv_bfloat16* cen, int* labels, int H, int N, int Cn,
                   int pin_begin, int pin_label, int* amb, int* d_status, cudaStream_t st);
 
+// Exact warp-per-row selection of the rows queued in fixq (select.cu).  fixq: per
+// head a count followed by (row, query cluster) pairs, H * (2 N + 1) ints.
+int launch_select_fix(const __nv_bfloat16* QU, const __nv_bfloat16* cks, const int* kcounts, const int* ns,
+                      int* unip, int* rowcnt, int H, int N, int CQ, const int* fixq, cudaStream_t st);
+
 }  // namespace t2t

@@ -1,0 +1,452 @@
+// Scoring + budgeted cluster selection + union on the tensor cores.
+//
+// The selection of a query is DEFINED on exact scores (fp32 fused-multiply-add
+// chain over k, rounded to fp16; see select.cu).  Evaluating 2048 chains per
+// query costs N * C * 32 FMAs.  Here one CTA owns one query cluster; for every
+// tile of 128 of its rows a tcgen05 MMA (128 x 128 x 32 per chunk of centroids,
+// all 2048 centroids resident in shared memory) gives approximate scores s~ in
+// TMEM, and each row is settled in three streaming passes over them:
+//
+//   P1  row maximum, minimum and mean;
+//   P2  size-weighted histogram of s~ over [mean, max] (refined if the threshold
+//       bucket is crowded) -> the bucket [x_lo, x_hi] in which the running token
+//       count first reaches ns;
+//   P3  clusters with s~ > x_hi + 2 e' are selected outright (their sizes are
+//       summed exactly), clusters with s~ in [x_lo - 2 e', x_hi + 2 e'] become
+//       candidates; candidates get their exact chain score and fp16 key and are
+//       walked in (key descending, index ascending) order until ns is reached.
+//
+// With |s~ - chain| <= e_i (see assign_tc.cu for the bound; e_i = 2^-14 ||q_i||
+// max_c ||cks_c||) and e' = e_i + half an fp16 ulp at the threshold, every
+// cluster above the window is strictly above the exact threshold key and every
+// cluster below it strictly below, so the result equals the all-exact rule bit
+// for bit.  Rows that do not fit the fast path (more than 32 candidates, no
+// convergence, non-finite scores) are queued for the exact warp-per-row kernel.
+#include "common.cuh"
+#include "internal.h"
+
+namespace t2t {
+
+constexpr int ST_THREADS = 512;
+constexpr int ST_CH = 128;                 // centroids per MMA chunk
+constexpr int ST_NCH = kC / ST_CH;         // 16
+constexpr int ST_B = 64;                   // histogram buckets
+constexpr int ST_CAP = 32;                 // candidates per row
+constexpr int ST_MAX_ITERS = 4;
+
+constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
+constexpr int OFF_A = OFF_CK + 1024 * 128;              // 128 rows x 128 B (first 64 B used)
+constexpr int OFF_HIST = OFF_A + 128 * 128;             // [ST_B][128] packed (size << 12 | count)
+constexpr int OFF_CAND = OFF_HIST + ST_B * 128 * 4;     // [128][ST_CAP] cluster | key << 16
+constexpr int OFF_SIZE = OFF_CAND + 128 * ST_CAP * 4;   // [2048] cluster sizes
+constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [3][4][128] per-group partial max / min / sum
+constexpr int OFF_ROW = OFF_PART + 3 * 4 * 128 * 4;     // [12][128] per-row scalars
+constexpr int OFF_MISC = OFF_ROW + 12 * 128 * 4;        // union words, barriers, ...
+constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
+
+enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3 };
+// per-row scalar slots
+enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG };
+
+__device__ __forceinline__ int key16_from_score(float s) {
+  unsigned u = __half_as_ushort(__float2half_rn(s));
+  u ^= ((u >> 15) & 1u) * 0x7FFFu;
+  return (int)((u ^ 0x8000u) & 0xFFFFu);
+}
+
+__device__ __forceinline__ void wg_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
+
+__global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
+    const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
+    const int* __restrict__ kcounts, const int* __restrict__ qperm, const int* __restrict__ tile_sizes,
+    const int* __restrict__ ns_ptr, int* __restrict__ unip, int* __restrict__ rowcnt, int N, int CQ, int pin_tail,
+    int* __restrict__ fixq, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sCk = base + OFF_CK, sA = base + OFF_A;
+  int* sHist = reinterpret_cast<int*>(sm + OFF_HIST);
+  uint32_t* sCand = reinterpret_cast<uint32_t*>(sm + OFF_CAND);
+  int* sSize = reinterpret_cast<int*>(sm + OFF_SIZE);
+  float* sPart = reinterpret_cast<float*>(sm + OFF_PART);
+  float* sRowF = reinterpret_cast<float*>(sm + OFF_ROW);
+  int* sRowI = reinterpret_cast<int*>(sm + OFF_ROW);
+  uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_MISC);              // [64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_MISC + 256);          // [4]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 288);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 292);
+  int* sCmax = reinterpret_cast<int*>(sm + OFF_MISC + 296);                   // max ||cks||^2 as int bits
+  int* sOff = reinterpret_cast<int*>(sm + OFF_MISC + 300);                    // first sorted row of this cluster
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = tid >> 7;            // column group: chunks g, g + 4, g + 8, g + 12
+  const int r = tid & 127;           // row of the tile = TMEM lane
+  const int h = blockIdx.y, t = blockIdx.x;
+  const __nv_bfloat16* ckh = cks + (size_t)h * kC * kR;
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    *sCmax = 0;
+    *sOff = 0;
+    for (int i = 0; i < 4; ++i) mbar_init(bars + i, 1);
+    mbar_init_fence();
+  }
+  if (tid < 64) sUnion[tid] = 0u;
+  // all 2048 centroids: 16-byte chunk id -> centroid id >> 2, chunk id & 3
+#pragma unroll
+  for (int i = 0; i < (kC * 4) / ST_THREADS; ++i) {
+    const int id = tid + ST_THREADS * i;
+    const int c = id >> 2, ch = id & 3;
+    cp_async16(sCk + sw128(c & 1023, (c >> 10) * 4 + ch), ckh + (size_t)c * kR + ch * 8, 16u);
+  }
+  cp_async_commit();
+  for (int c = tid; c < kC; c += ST_THREADS) sSize[c] = kcounts[(size_t)h * kC + c];
+  __syncthreads();
+  {
+    int part = 0;
+    for (int c = tid; c < t; c += ST_THREADS) part += tile_sizes[(size_t)h * CQ + c];
+    part = __reduce_add_sync(0xffffffffu, part);
+    if (lane == 0 && part) atomicAdd(sOff, part);
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+  {
+    // largest squared norm of a scoring centroid
+    float mx = 0.f;
+    for (int c = tid; c < kC; c += ST_THREADS) {
+      float s = 0.f;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_CK + sw128(c & 1023, (c >> 10) * 4 + q4));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          s = fmaf(bf_lo(ws[e]), bf_lo(ws[e]), s);
+          s = fmaf(bf_hi(ws[e]), bf_hi(ws[e]), s);
+        }
+      }
+      mx = fmaxf(mx, s);
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+    if (lane == 0) atomicMax(sCmax, __float_as_int(mx));
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, g * ST_CH);
+  const int ns = *ns_ptr;
+  const int off = *sOff;
+  const int nrows = tile_sizes[(size_t)h * CQ + t];
+  const float cmaxnorm = sqrtf(__int_as_float(*sCmax));
+  constexpr uint32_t idesc = make_idesc_bf16(128, ST_CH, false, false);
+  uint32_t ph = 0;
+  bool dead = false;
+
+  // Streams this group's four chunks through its TMEM buffer; body(cbase, v)
+  // sees 32 consecutive approximate scores of this thread's row.
+  auto stream = [&](auto&& body) {
+#pragma unroll 1
+    for (int i = 0; i < ST_NCH / 4 && !dead; ++i) {
+      const int cc = g + 4 * i;
+      if (r == 0) {
+        tc_fence_after();
+#pragma unroll
+        for (int s2 = 0; s2 < 2; ++s2)
+          umma_ss(tmem + g * ST_CH, make_sdesc(sA + s2 * 32, 16, 1024),
+                  make_sdesc(sCk + (cc & 7) * (ST_CH * 128) + (cc >> 3) * 64 + s2 * 32, 16, 1024), idesc,
+                  s2 > 0 ? 1u : 0u);
+        umma_commit(bars + g);
+      }
+      if (!mbar_wait(bars + g, ph, abort_flag)) { dead = true; break; }
+      ph ^= 1u;
+      tc_fence_after();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t v[32];
+        tmem_ld32(t_lane + q * 32, v);
+        tmem_wait_ld();
+        body(cc * ST_CH + q * 32, v);
+      }
+      tc_fence_before();
+      wg_sync(g);          // all four warps of the group are done with the buffer
+    }
+  };
+
+  for (int r0 = 0; r0 < nrows; r0 += 128) {
+    const int rows_here = min(128, nrows - r0);
+    // previous tile fully consumed; a group whose wait gave up takes the whole CTA out here, so every
+    // barrier below is reached by all threads or by none
+    if (__syncthreads_or(dead ? 1 : 0)) break;
+    {
+      const int ar = tid >> 2, ch = tid & 3;
+      const bool valid = ar < rows_here;
+      const int orig = valid ? qperm[(size_t)h * N + off + r0 + ar] : 0;
+      cp_async16(sA + sw128(ar, ch), QU + ((size_t)h * N + orig) * kR + ch * 8, valid ? 16u : 0u);
+      cp_async_commit();
+      if (ch == 0) sRowI[R_ORIG * 128 + ar] = orig;
+    }
+    cp_async_wait<0>();
+    fence_proxy_async();
+    tc_fence_before();
+    __syncthreads();
+    if (g == 0) {
+      float qn = 0.f;
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, q4));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          qn = fmaf(bf_lo(ws[e]), bf_lo(ws[e]), qn);
+          qn = fmaf(bf_hi(ws[e]), bf_hi(ws[e]), qn);
+        }
+      }
+      sRowF[R_EPS * 128 + r] = 6.103515625e-05f * sqrtf(qn) * cmaxnorm + 1.0e-30f;
+      sRowI[R_STATE * 128 + r] = r < rows_here ? RS_SEARCH : RS_DONE;
+      sRowI[R_CUM * 128 + r] = 0;
+      sRowI[R_NCAND * 128 + r] = 0;
+      sRowI[R_SIZEA * 128 + r] = 0;
+    }
+
+    // ---- P1: row statistics -------------------------------------------------
+    {
+      float mx0 = -INFINITY, mx1 = -INFINITY, mn0 = INFINITY, mn1 = INFINITY, s0 = 0.f, s1 = 0.f;
+      stream([&](int, const uint32_t(&v)[32]) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          const float a = __uint_as_float(v[j]), b = __uint_as_float(v[j + 1]);
+          mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
+          mn0 = fminf(mn0, a); mn1 = fminf(mn1, b);
+          s0 += a; s1 += b;
+        }
+      });
+      sPart[(0 * 4 + g) * 128 + r] = fmaxf(mx0, mx1);
+      sPart[(1 * 4 + g) * 128 + r] = fminf(mn0, mn1);
+      sPart[(2 * 4 + g) * 128 + r] = s0 + s1;
+    }
+    __syncthreads();
+    if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
+      float M = -INFINITY, mn = INFINITY, sum = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 4; ++gg) {
+        M = fmaxf(M, sPart[(0 * 4 + gg) * 128 + r]);
+        mn = fminf(mn, sPart[(1 * 4 + gg) * 128 + r]);
+        sum += sPart[(2 * 4 + gg) * 128 + r];
+      }
+      const float mean = sum * (1.0f / kC);
+      const bool finite = fabsf(M) < INFINITY && fabsf(mn) < INFINITY && fabsf(mean) < INFINITY;
+      const float lo = fminf(mean, M);
+      sRowF[R_HI * 128 + r] = M;
+      sRowF[R_LO * 128 + r] = lo;
+      sRowF[R_MIN * 128 + r] = mn;
+      sRowF[R_INV * 128 + r] = M > lo ? (float)ST_B / (M - lo) : 0.f;
+      if (!finite) sRowI[R_STATE * 128 + r] = RS_QUEUE;
+    }
+
+    // ---- P2: histogram search for the threshold bucket --------------------------
+    for (int it = 0; it < ST_MAX_ITERS; ++it) {
+      for (int i = tid; i < ST_B * 128; i += ST_THREADS) sHist[i] = 0;
+      __syncthreads();
+      {
+        const bool act = sRowI[R_STATE * 128 + r] == RS_SEARCH;
+        const float hi = sRowF[R_HI * 128 + r], lo = sRowF[R_LO * 128 + r], inv = sRowF[R_INV * 128 + r];
+        const float hinv = hi * inv;
+        stream([&](int cbase, const uint32_t(&v)[32]) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float a = __uint_as_float(v[j]);
+            int b = (int)fmaf(-a, inv, hinv);
+            b = b > ST_B - 1 ? ST_B - 1 : b;
+            if (act && a <= hi && a >= lo) atomicAdd(&sHist[b * 128 + r], (sSize[cbase + j] << 12) + 1);
+          }
+        });
+      }
+      __syncthreads();
+      int searching = 0;
+      if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
+        const float hi = sRowF[R_HI * 128 + r], lo = sRowF[R_LO * 128 + r];
+        const float eps = sRowF[R_EPS * 128 + r];
+        int cum = sRowI[R_CUM * 128 + r];
+        int bstar = -1, cnt = 0;
+        for (int b = 0; b < ST_B; ++b) {
+          const int p = sHist[b * 128 + r];
+          if (cum + (p >> 12) >= ns) { bstar = b; cnt = p & 4095; break; }
+          cum += p >> 12;
+        }
+        const float w = (hi - lo) * (1.0f / ST_B);
+        if (bstar < 0) {
+          // the threshold lies below this range: continue from its lower end down to the row minimum
+          const float mn = sRowF[R_MIN * 128 + r];
+          if (lo > mn && it + 1 < ST_MAX_ITERS) {
+            sRowI[R_CUM * 128 + r] = cum;
+            sRowF[R_HI * 128 + r] = lo;
+            sRowF[R_LO * 128 + r] = mn;
+            sRowF[R_INV * 128 + r] = (float)ST_B / (lo - mn);
+            searching = 1;
+          } else {
+            sRowI[R_STATE * 128 + r] = RS_QUEUE;
+          }
+        } else {
+          const float x_hi = hi - (float)bstar * w, x_lo = hi - (float)(bstar + 1) * w;
+          // 2^-10 |x|: half an fp16 ulp even if the threshold sits just across a power of two
+          const float e2 = 2.0f * (eps + 9.765625e-04f * fmaxf(fabsf(x_lo), fabsf(x_hi)) + 5.9604645e-08f);
+          if (cnt > ST_CAP / 2 && it + 1 < ST_MAX_ITERS && w > 2.0f * e2) {
+            sRowI[R_CUM * 128 + r] = cum;            // sizes above the bucket are settled
+            sRowF[R_HI * 128 + r] = x_hi;
+            sRowF[R_LO * 128 + r] = x_lo;
+            sRowF[R_INV * 128 + r] = (float)ST_B / (x_hi - x_lo);
+            searching = 1;
+          } else {
+            sRowF[R_THRA * 128 + r] = x_hi + e2;
+            sRowF[R_THRW * 128 + r] = x_lo - e2;
+            sRowI[R_STATE * 128 + r] = RS_COLLECT;
+          }
+        }
+      }
+      if (!__syncthreads_or(searching)) break;
+    }
+    if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) sRowI[R_STATE * 128 + r] = RS_QUEUE;
+    __syncthreads();
+
+    // ---- P3: select above the window, collect candidates inside it ---------------
+    {
+      const bool act = sRowI[R_STATE * 128 + r] == RS_COLLECT;
+      const float thrA = sRowF[R_THRA * 128 + r], thrW = sRowF[R_THRW * 128 + r];
+      int sizeA = 0;
+      stream([&](int cbase, const uint32_t(&v)[32]) {
+        uint32_t wbits = 0u;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float a = __uint_as_float(v[j]);
+          const bool above = act && a > thrA;
+          const bool cand = act && !above && a >= thrW;
+          if (above) sizeA += sSize[cbase + j];
+          if (cand) {
+            const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
+            if (slot < ST_CAP) sCand[r * ST_CAP + slot] = (uint32_t)(cbase + j);
+          }
+          wbits |= __ballot_sync(0xffffffffu, above) ? (1u << j) : 0u;
+        }
+        if (lane == 0 && wbits && (sUnion[cbase >> 5] & wbits) != wbits) atomicOr(&sUnion[cbase >> 5], wbits);
+      });
+      if (sizeA) atomicAdd(&sRowI[R_SIZEA * 128 + r], sizeA);
+    }
+    __syncthreads();
+
+    // ---- exact keys of the candidates (four threads share a row) ------------------
+    {
+      const int st = sRowI[R_STATE * 128 + r];
+      const int n = sRowI[R_NCAND * 128 + r];
+      if (st == RS_COLLECT && n <= ST_CAP && g < n) {
+        float q[kR];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, q4));
+          q[8 * q4 + 0] = bf_lo(w.x); q[8 * q4 + 1] = bf_hi(w.x);
+          q[8 * q4 + 2] = bf_lo(w.y); q[8 * q4 + 3] = bf_hi(w.y);
+          q[8 * q4 + 4] = bf_lo(w.z); q[8 * q4 + 5] = bf_hi(w.z);
+          q[8 * q4 + 6] = bf_lo(w.w); q[8 * q4 + 7] = bf_hi(w.w);
+        }
+        for (int slot = g; slot < n; slot += 4) {
+          const int c = (int)(sCand[r * ST_CAP + slot] & 0xFFFFu);
+          float acc = 0.f;
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4) {
+            const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_CK + sw128(c & 1023, (c >> 10) * 4 + q4));
+            acc = fmaf(q[8 * q4 + 0], bf_lo(w.x), acc); acc = fmaf(q[8 * q4 + 1], bf_hi(w.x), acc);
+            acc = fmaf(q[8 * q4 + 2], bf_lo(w.y), acc); acc = fmaf(q[8 * q4 + 3], bf_hi(w.y), acc);
+            acc = fmaf(q[8 * q4 + 4], bf_lo(w.z), acc); acc = fmaf(q[8 * q4 + 5], bf_hi(w.z), acc);
+            acc = fmaf(q[8 * q4 + 6], bf_lo(w.w), acc); acc = fmaf(q[8 * q4 + 7], bf_hi(w.w), acc);
+          }
+          sCand[r * ST_CAP + slot] = (uint32_t)c | ((uint32_t)key16_from_score(acc) << 16);
+        }
+      }
+    }
+    __syncthreads();
+
+    // ---- walk the candidates in exact order; queue what could not be settled -------
+    if (g == 0) {
+      int st = sRowI[R_STATE * 128 + r];
+      const int n = sRowI[R_NCAND * 128 + r];
+      const int orig = sRowI[R_ORIG * 128 + r];
+      if (st == RS_COLLECT) {
+        int running = sRowI[R_SIZEA * 128 + r];
+        if (n > ST_CAP || running >= ns) {
+          st = RS_QUEUE;
+        } else {
+          uint32_t used = 0u;
+          int rc = -1;
+          while (running < ns) {
+            int best = -1;
+            uint32_t bkey = 0u, bidx = 0u;
+            for (int s2 = 0; s2 < n; ++s2) {
+              if ((used >> s2) & 1u) continue;
+              const uint32_t e = sCand[r * ST_CAP + s2];
+              const uint32_t k = e >> 16, c = e & 0xFFFFu;
+              if (best < 0 || k > bkey || (k == bkey && c < bidx)) { best = s2; bkey = k; bidx = c; }
+            }
+            if (best < 0) break;
+            used |= 1u << best;
+            const int sz = sSize[bidx];
+            const uint32_t bit = 1u << (bidx & 31);
+            if (!(sUnion[bidx >> 5] & bit)) atomicOr(&sUnion[bidx >> 5], bit);
+            if (running + sz >= ns) rc = running + sz;
+            running += sz;
+          }
+          if (rc < 0) st = RS_QUEUE;      // the window did not reach the budget: let the exact kernel decide
+          else rowcnt[(size_t)h * N + orig] = rc;
+        }
+      }
+      if (st == RS_QUEUE) {
+        int* qh = fixq + (size_t)h * (2 * (size_t)N + 1);
+        const int slot = atomicAdd(qh, 1);
+        qh[1 + 2 * slot] = orig;
+        qh[2 + 2 * slot] = t;
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < 64) {
+    uint32_t w = sUnion[tid];
+    if (pin_tail > 0 && tid == 63) w |= 0x80000000u;
+    unip[((size_t)h * CQ + t) * 64 + tid] = (int)w;
+  }
+  if (*abort_flag && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+size_t select_ws_bytes(int H, int N) { return (size_t)H * (2 * (size_t)N + 1) * sizeof(int); }
+
+}  // namespace t2t
+
+using namespace t2t;
+
+extern "C" size_t t2t_score_select_union_ws_bytes(int H, int N) { return select_ws_bytes(H, N); }
+
+extern "C" int t2t_score_select_union(const void* QU, const void* cks, const void* kcounts, const void* qperm,
+                                      const void* tile_sizes, const int* ns, void* unip, void* rowcnt, int H,
+                                      int N, int CQ, int pin_tail, void* ws, size_t ws_bytes, int* d_status,
+                                      cudaStream_t st) {
+  if (!QU || !cks || !kcounts || !qperm || !tile_sizes || !ns || !unip || !rowcnt || !ws) return T2T_ERR_ARG;
+  if (H <= 0 || N <= 0 || CQ <= 0 || N >= (1 << 19)) return T2T_ERR_ARG;
+  if (ws_bytes < select_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  int* fixq = (int*)ws;
+  if (cudaMemsetAsync(fixq, 0, select_ws_bytes(H, N), st) != cudaSuccess) return T2T_ERR_CUDA;
+  if (cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM) != cudaSuccess)
+    return T2T_ERR_CUDA;
+  select_tc_kernel<<<dim3(CQ, H), ST_THREADS, ST_SMEM, st>>>(
+      (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const int*)qperm,
+      (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, pin_tail, fixq, d_status);
+  if (cudaGetLastError() != cudaSuccess) return T2T_ERR_CUDA;
+  return launch_select_fix((const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, ns, (int*)unip,
+                           (int*)rowcnt, H, N, CQ, fixq, st);
+}

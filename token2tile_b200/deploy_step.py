@@ -145,7 +145,8 @@ class MaskedStepDeploy:
         self._tile_attn_plan_ints = int(L.t2t_tile_attn_plan_ints(H, N, CQ))
         ws = max(int(L.t2t_kmeans_maintain_ws_bytes(H, N, CQ, C)),
                  int(L.t2t_vstats_gather_ws_bytes(H, C)),
-                 int(L.t2t_centroid_update_ws_bytes(H, N, C)), int(L.t2t_assign_ws_bytes(H, N)))
+                 int(L.t2t_centroid_update_ws_bytes(H, N, C)), int(L.t2t_assign_ws_bytes(H, N)),
+                 int(L.t2t_score_select_union_ws_bytes(H, N)))
         self._ws = e(ws, dtype=torch.uint8)
         self._attn_ws = e(int(L.t2t_tile_attn_ws_bytes(H, N)), dtype=torch.uint8)
         self._struct = self._new_structure()      # structure of unannotated calls
@@ -321,8 +322,8 @@ class MaskedStepDeploy:
                 self._mark("kmeans")
                 check(L.t2t_score_select_union(
                     ptr(self.QU), ptr(S["cks"]), ptr(S["counts"]), ptr(S["qperm"]), ptr(S["tile_sizes"]),
-                    ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, st),
-                    "t2t_score_select_union")
+                    ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, ptr(self._ws),
+                    self._ws.numel(), ptr(self.status), st), "t2t_score_select_union")
                 self._mark("select")
                 S["Uq"] = state["Uq"]
                 S["step"] = self._cfg_step
