@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(SEL_THREADS, 1) select_fix_kernel(
   __syncthreads();
   const int ns = *ns_ptr;
   for (int e = blockIdx.x * SEL_WARPS + warp; e < count; e += gridDim.x * SEL_WARPS) {
-    const int row = q[1 + 2 * e], t = q[2 + 2 * e];
+    const int row = q[1 + 2 * e], t = q[2 + 2 * e] & 0xFFFFFF;      // top byte: why the fast kernel queued it
     const float qv = bf_to_f(QU[((size_t)h * N + row) * kR + lane]);
     uint32_t gA, gB;
     int rc;

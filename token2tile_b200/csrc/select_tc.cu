@@ -7,7 +7,8 @@
 // all 2048 centroids resident in shared memory) gives approximate scores s~ in
 // TMEM, and each row is settled in three streaming passes over them:
 //
-//   P1  row maximum, minimum and mean;
+//   P1  row maximum (the row mean is q . mean centroid, the minimum is bounded by
+//       -||q|| max ||c||, neither needs a pass);
 //   P2  size-weighted histogram of s~ over [mean, max] (refined if the threshold
 //       bucket is crowded) -> the bucket [x_lo, x_hi] in which the running token
 //       count first reaches ns;
@@ -20,7 +21,7 @@
 // max_c ||cks_c||) and e' = e_i + half an fp16 ulp at the threshold, every
 // cluster above the window is strictly above the exact threshold key and every
 // cluster below it strictly below, so the result equals the all-exact rule bit
-// for bit.  Rows that do not fit the fast path (more than 32 candidates, no
+// for bit.  Rows that do not fit the fast path (more than 64 candidates, no
 // convergence, non-finite scores) are queued for the exact warp-per-row kernel.
 #include "common.cuh"
 #include "internal.h"
@@ -31,28 +32,32 @@ constexpr int ST_THREADS = 512;
 constexpr int ST_CH = 128;                 // centroids per MMA chunk
 constexpr int ST_NCH = kC / ST_CH;         // 16
 constexpr int ST_B = 64;                   // histogram buckets
-constexpr int ST_CAP = 32;                 // candidates per row
+constexpr int ST_CAP = 64;                 // candidates per row
+constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
 constexpr int ST_MAX_ITERS = 4;
 
 constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
 constexpr int OFF_A = OFF_CK + 1024 * 128;              // 128 rows x 128 B (first 64 B used)
-constexpr int OFF_HIST = OFF_A + 128 * 128;             // [ST_B][128] packed (size << 12 | count)
-constexpr int OFF_CAND = OFF_HIST + ST_B * 128 * 4;     // [128][ST_CAP] cluster | key << 16
-constexpr int OFF_SIZE = OFF_CAND + 128 * ST_CAP * 4;   // [2048] cluster sizes
-constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [3][4][128] per-group partial max / min / sum
-constexpr int OFF_ROW = OFF_PART + 3 * 4 * 128 * 4;     // [12][128] per-row scalars
-constexpr int OFF_MISC = OFF_ROW + 12 * 128 * 4;        // union words, barriers, ...
+constexpr int OFF_HIST = OFF_A + 128 * 128;             // [ST_B][128] packed (size << 12 | count); after P2 the
+constexpr int OFF_CAND = OFF_HIST;                      //   same bytes hold [128][ST_CAP] cluster | key << 16
+constexpr int OFF_SIZE = OFF_HIST + ST_B * 128 * 4;     // [2048] (cluster size << 12) + 1
+constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [4][128] per-group partial maxima, then [32] mean centroid
+constexpr int OFF_ROW = OFF_PART + 4 * 128 * 4 + 32 * 4;  // [12][128] per-row scalars
+constexpr int OFF_MISC = OFF_ROW + 13 * 128 * 4;        // union words, barriers, ...
 constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
 
+// RS_QUEUE + k: queued for the exact kernel; k says why (1 non-finite scores, 2 threshold not bracketed,
+// 3 too many candidates, 4 budget met above the window, 5 / 6 threshold outside the window, 7 walk ran dry)
 enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3 };
 // per-row scalar slots
-enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG };
+enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2 };
 
-__device__ __forceinline__ int key16_from_score(float s) {
-  unsigned u = __half_as_ushort(__float2half_rn(s));
+__device__ __forceinline__ int key16_from_half(__half hv) {
+  unsigned u = __half_as_ushort(hv);
   u ^= ((u >> 15) & 1u) * 0x7FFFu;
   return (int)((u ^ 0x8000u) & 0xFFFFu);
 }
+__device__ __forceinline__ int key16_from_score(float s) { return key16_from_half(__float2half_rn(s)); }
 
 __device__ __forceinline__ void wg_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
 
@@ -67,8 +72,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   const uint32_t sCk = base + OFF_CK, sA = base + OFF_A;
   int* sHist = reinterpret_cast<int*>(sm + OFF_HIST);
   uint32_t* sCand = reinterpret_cast<uint32_t*>(sm + OFF_CAND);
-  int* sSize = reinterpret_cast<int*>(sm + OFF_SIZE);
+  int* sSizeP = reinterpret_cast<int*>(sm + OFF_SIZE);
   float* sPart = reinterpret_cast<float*>(sm + OFF_PART);
+  float* sCbar = sPart + 4 * 128;
   float* sRowF = reinterpret_cast<float*>(sm + OFF_ROW);
   int* sRowI = reinterpret_cast<int*>(sm + OFF_ROW);
   uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_MISC);              // [64]
@@ -104,7 +110,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     cp_async16(sCk + sw128(c & 1023, (c >> 10) * 4 + ch), ckh + (size_t)c * kR + ch * 8, 16u);
   }
   cp_async_commit();
-  for (int c = tid; c < kC; c += ST_THREADS) sSize[c] = kcounts[(size_t)h * kC + c];
+  for (int c = tid; c < kC; c += ST_THREADS) sSizeP[c] = (kcounts[(size_t)h * kC + c] << 12) + 1;
+  if (tid < 32) sCbar[tid] = 0.f;
   __syncthreads();
   {
     int part = 0;
@@ -134,6 +141,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
     if (lane == 0) atomicMax(sCmax, __float_as_int(mx));
+    // mean centroid (only places the histogram range, so the summation order does not matter)
+    const int d = tid & 31, sub = tid >> 5;
+    float acc = 0.f;
+    for (int c = sub * 128; c < sub * 128 + 128; ++c)
+      acc += bf_to_f(*reinterpret_cast<const __nv_bfloat16*>(sm + OFF_CK + sw128(c & 1023, (c >> 10) * 4 + (d >> 3)) +
+                                                            (d & 7) * 2));
+    atomicAdd(&sCbar[d], acc * (1.0f / kC));
   }
   fence_proxy_async();
   tc_fence_before();
@@ -197,57 +211,54 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     tc_fence_before();
     __syncthreads();
     if (g == 0) {
-      float qn = 0.f;
+      float qn = 0.f, mean = 0.f;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, q4));
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          qn = fmaf(bf_lo(ws[e]), bf_lo(ws[e]), qn);
-          qn = fmaf(bf_hi(ws[e]), bf_hi(ws[e]), qn);
+          const float lo = bf_lo(ws[e]), hi = bf_hi(ws[e]);
+          qn = fmaf(lo, lo, qn);
+          qn = fmaf(hi, hi, qn);
+          mean = fmaf(lo, sCbar[q4 * 8 + e * 2], mean);
+          mean = fmaf(hi, sCbar[q4 * 8 + e * 2 + 1], mean);
         }
       }
-      sRowF[R_EPS * 128 + r] = 6.103515625e-05f * sqrtf(qn) * cmaxnorm + 1.0e-30f;
+      const float bound = sqrtf(qn) * cmaxnorm;
+      sRowF[R_EPS * 128 + r] = 6.103515625e-05f * bound + 1.0e-30f;
+      sRowF[R_LO * 128 + r] = mean;
+      sRowF[R_MIN * 128 + r] = -bound;
       sRowI[R_STATE * 128 + r] = r < rows_here ? RS_SEARCH : RS_DONE;
       sRowI[R_CUM * 128 + r] = 0;
       sRowI[R_NCAND * 128 + r] = 0;
       sRowI[R_SIZEA * 128 + r] = 0;
     }
 
-    // ---- P1: row statistics -------------------------------------------------
+    // ---- P1: row maximum --------------------------------------------------------
     {
-      float mx0 = -INFINITY, mx1 = -INFINITY, mn0 = INFINITY, mn1 = INFINITY, s0 = 0.f, s1 = 0.f;
+      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
       stream([&](int, const uint32_t(&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float a = __uint_as_float(v[j]), b = __uint_as_float(v[j + 1]);
-          mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b);
-          mn0 = fminf(mn0, a); mn1 = fminf(mn1, b);
-          s0 += a; s1 += b;
+        for (int j = 0; j < 32; j += 4) {
+          mx0 = fmaxf(mx0, __uint_as_float(v[j]));
+          mx1 = fmaxf(mx1, __uint_as_float(v[j + 1]));
+          mx2 = fmaxf(mx2, __uint_as_float(v[j + 2]));
+          mx3 = fmaxf(mx3, __uint_as_float(v[j + 3]));
         }
       });
-      sPart[(0 * 4 + g) * 128 + r] = fmaxf(mx0, mx1);
-      sPart[(1 * 4 + g) * 128 + r] = fminf(mn0, mn1);
-      sPart[(2 * 4 + g) * 128 + r] = s0 + s1;
+      sPart[g * 128 + r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
     }
     __syncthreads();
     if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
-      float M = -INFINITY, mn = INFINITY, sum = 0.f;
-#pragma unroll
-      for (int gg = 0; gg < 4; ++gg) {
-        M = fmaxf(M, sPart[(0 * 4 + gg) * 128 + r]);
-        mn = fminf(mn, sPart[(1 * 4 + gg) * 128 + r]);
-        sum += sPart[(2 * 4 + gg) * 128 + r];
-      }
-      const float mean = sum * (1.0f / kC);
-      const bool finite = fabsf(M) < INFINITY && fabsf(mn) < INFINITY && fabsf(mean) < INFINITY;
+      const float M = fmaxf(fmaxf(sPart[r], sPart[128 + r]), fmaxf(sPart[256 + r], sPart[384 + r]));
+      const float mean = sRowF[R_LO * 128 + r];
+      const bool finite = fabsf(M) < INFINITY && fabsf(mean) < INFINITY;
       const float lo = fminf(mean, M);
       sRowF[R_HI * 128 + r] = M;
       sRowF[R_LO * 128 + r] = lo;
-      sRowF[R_MIN * 128 + r] = mn;
       sRowF[R_INV * 128 + r] = M > lo ? (float)ST_B / (M - lo) : 0.f;
-      if (!finite) sRowI[R_STATE * 128 + r] = RS_QUEUE;
+      if (!finite) sRowI[R_STATE * 128 + r] = RS_QUEUE + 1;
     }
 
     // ---- P2: histogram search for the threshold bucket --------------------------
@@ -255,16 +266,22 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       for (int i = tid; i < ST_B * 128; i += ST_THREADS) sHist[i] = 0;
       __syncthreads();
       {
+        // bucket = floor((hi - s) * inv): the subtraction first, so that s == hi gives exactly 0 and s > hi
+        // a negative bucket; rows that are not searching get hi = -inf and fall out the same way
         const bool act = sRowI[R_STATE * 128 + r] == RS_SEARCH;
-        const float hi = sRowF[R_HI * 128 + r], lo = sRowF[R_LO * 128 + r], inv = sRowF[R_INV * 128 + r];
-        const float hinv = hi * inv;
+        const float hi = act ? sRowF[R_HI * 128 + r] : -INFINITY;
+        const float inv = act ? sRowF[R_INV * 128 + r] : 1.0f;
+        int* hist_r = sHist + r;
         stream([&](int cbase, const uint32_t(&v)[32]) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float a = __uint_as_float(v[j]);
-            int b = (int)fmaf(-a, inv, hinv);
-            b = b > ST_B - 1 ? ST_B - 1 : b;
-            if (act && a <= hi && a >= lo) atomicAdd(&sHist[b * 128 + r], (sSize[cbase + j] << 12) + 1);
+          for (int j4 = 0; j4 < 32; j4 += 4) {
+            const int4 p4 = *reinterpret_cast<const int4*>(sSizeP + cbase + j4);
+            const int pp[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int b = __float2int_rd((hi - __uint_as_float(v[j4 + e])) * inv);
+              if ((unsigned)b < (unsigned)ST_B) atomicAdd(hist_r + b * 128, pp[e]);
+            }
           }
         });
       }
@@ -291,13 +308,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             sRowF[R_INV * 128 + r] = (float)ST_B / (lo - mn);
             searching = 1;
           } else {
-            sRowI[R_STATE * 128 + r] = RS_QUEUE;
+            sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
           }
         } else {
           const float x_hi = hi - (float)bstar * w, x_lo = hi - (float)(bstar + 1) * w;
           // 2^-10 |x|: half an fp16 ulp even if the threshold sits just across a power of two
           const float e2 = 2.0f * (eps + 9.765625e-04f * fmaxf(fabsf(x_lo), fabsf(x_hi)) + 5.9604645e-08f);
-          if (cnt > ST_CAP / 2 && it + 1 < ST_MAX_ITERS && w > 2.0f * e2) {
+          if (cnt > ST_REFINE && it + 1 < ST_MAX_ITERS && w > 2.0f * e2) {
             sRowI[R_CUM * 128 + r] = cum;            // sizes above the bucket are settled
             sRowF[R_HI * 128 + r] = x_hi;
             sRowF[R_LO * 128 + r] = x_lo;
@@ -306,37 +323,43 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
           } else {
             sRowF[R_THRA * 128 + r] = x_hi + e2;
             sRowF[R_THRW * 128 + r] = x_lo - e2;
+            sRowF[R_E2 * 128 + r] = e2;
             sRowI[R_STATE * 128 + r] = RS_COLLECT;
           }
         }
       }
       if (!__syncthreads_or(searching)) break;
     }
-    if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) sRowI[R_STATE * 128 + r] = RS_QUEUE;
+    if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
     __syncthreads();
 
     // ---- P3: select above the window, collect candidates inside it ---------------
     {
       const bool act = sRowI[R_STATE * 128 + r] == RS_COLLECT;
-      const float thrA = sRowF[R_THRA * 128 + r], thrW = sRowF[R_THRW * 128 + r];
-      int sizeA = 0;
+      const float thrA = act ? sRowF[R_THRA * 128 + r] : INFINITY;
+      const float thrW = act ? sRowF[R_THRW * 128 + r] : INFINITY;
+      int sumA = 0;      // packed: (sizes << 12) + count
       stream([&](int cbase, const uint32_t(&v)[32]) {
         uint32_t wbits = 0u;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float a = __uint_as_float(v[j]);
-          const bool above = act && a > thrA;
-          const bool cand = act && !above && a >= thrW;
-          if (above) sizeA += sSize[cbase + j];
-          if (cand) {
-            const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
-            if (slot < ST_CAP) sCand[r * ST_CAP + slot] = (uint32_t)(cbase + j);
+        for (int j4 = 0; j4 < 32; j4 += 4) {
+          const int4 p4 = *reinterpret_cast<const int4*>(sSizeP + cbase + j4);
+          const int pp[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a = __uint_as_float(v[j4 + e]);
+            const bool above = a > thrA;
+            sumA += above ? pp[e] : 0;
+            if (!above && a >= thrW) {
+              const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
+              if (slot < ST_CAP) sCand[r * ST_CAP + slot] = (uint32_t)(cbase + j4 + e);
+            }
+            wbits |= __ballot_sync(0xffffffffu, above) ? (1u << (j4 + e)) : 0u;
           }
-          wbits |= __ballot_sync(0xffffffffu, above) ? (1u << j) : 0u;
         }
         if (lane == 0 && wbits && (sUnion[cbase >> 5] & wbits) != wbits) atomicOr(&sUnion[cbase >> 5], wbits);
       });
-      if (sizeA) atomicAdd(&sRowI[R_SIZEA * 128 + r], sizeA);
+      if (sumA) atomicAdd(&sRowI[R_SIZEA * 128 + r], sumA >> 12);
     }
     __syncthreads();
 
@@ -378,37 +401,54 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       const int orig = sRowI[R_ORIG * 128 + r];
       if (st == RS_COLLECT) {
         int running = sRowI[R_SIZEA * 128 + r];
-        if (n > ST_CAP || running >= ns) {
-          st = RS_QUEUE;
+        // Independent of how the window was found, the result is exact iff the exact threshold key lies
+        // inside it: fewer than ns tokens have a key >= y = thrA - e' (every cluster above the window does,
+        // plus the candidates counted here), and at least ns have a key >= z = thrW + e'.
+        int why = n > ST_CAP ? 3 : (running >= ns ? 4 : 0);
+        if (!why) {
+          const float e1 = 0.5f * sRowF[R_E2 * 128 + r];
+          const uint32_t ky = (uint32_t)key16_from_half(__float2half_ru(sRowF[R_THRA * 128 + r] - e1));
+          const uint32_t kz = (uint32_t)key16_from_half(__float2half_ru(sRowF[R_THRW * 128 + r] + e1));
+          int sy = running, sz2 = running;
+          for (int s2 = 0; s2 < n; ++s2) {
+            const uint32_t e = sCand[r * ST_CAP + s2];
+            const int szc = sSizeP[e & 0xFFFFu] >> 12;
+            sy += (e >> 16) >= ky ? szc : 0;
+            sz2 += (e >> 16) >= kz ? szc : 0;
+          }
+          why = sy >= ns ? 5 : (sz2 < ns ? 6 : 0);
+        }
+        if (why) {
+          st = RS_QUEUE + why;
         } else {
-          uint32_t used = 0u;
+          unsigned long long used = 0ull;
           int rc = -1;
           while (running < ns) {
             int best = -1;
             uint32_t bkey = 0u, bidx = 0u;
             for (int s2 = 0; s2 < n; ++s2) {
-              if ((used >> s2) & 1u) continue;
+              if ((used >> s2) & 1ull) continue;
               const uint32_t e = sCand[r * ST_CAP + s2];
               const uint32_t k = e >> 16, c = e & 0xFFFFu;
               if (best < 0 || k > bkey || (k == bkey && c < bidx)) { best = s2; bkey = k; bidx = c; }
             }
             if (best < 0) break;
-            used |= 1u << best;
-            const int sz = sSize[bidx];
+            used |= 1ull << best;
+            const int sz = sSizeP[bidx] >> 12;
             const uint32_t bit = 1u << (bidx & 31);
             if (!(sUnion[bidx >> 5] & bit)) atomicOr(&sUnion[bidx >> 5], bit);
             if (running + sz >= ns) rc = running + sz;
             running += sz;
           }
-          if (rc < 0) st = RS_QUEUE;      // the window did not reach the budget: let the exact kernel decide
+          if (rc < 0) st = RS_QUEUE + 7;  // the window did not reach the budget: let the exact kernel decide
           else rowcnt[(size_t)h * N + orig] = rc;
         }
       }
-      if (st == RS_QUEUE) {
+      if (st >= RS_QUEUE) {
         int* qh = fixq + (size_t)h * (2 * (size_t)N + 1);
         const int slot = atomicAdd(qh, 1);
         qh[1 + 2 * slot] = orig;
-        qh[2 + 2 * slot] = t;
+        qh[2 + 2 * slot] = t | ((st - RS_QUEUE) << 24);      // the reason rides in the top byte
       }
     }
   }
