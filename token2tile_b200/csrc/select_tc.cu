@@ -2,10 +2,13 @@
 //
 // The selection of a query is DEFINED on exact scores (fp32 fused-multiply-add
 // chain over k, rounded to fp16; see select.cu).  Evaluating 2048 chains per
-// query costs N * C * 32 FMAs.  Here one CTA owns one query cluster; for every
-// tile of 128 of its rows a tcgen05 MMA (128 x 128 x 32 per chunk of centroids,
-// all 2048 centroids resident in shared memory) gives approximate scores s~ in
-// TMEM, and each row is settled in three streaming passes over them:
+// query costs N * C * 32 FMAs.  Here one CTA owns 128 consecutive rows of the
+// cluster-sorted query order (a tile may span several query clusters: the rows
+// of cluster k form "segment" k of the tile and selections are OR-ed into the
+// segment's bitmap, flushed to the cluster's bitmap at the end).  A tcgen05 MMA
+// (128 x 128 x 32 per chunk of centroids, all 2048 centroids resident in shared
+// memory) gives approximate scores s~ in TMEM, and each row is settled in three
+// streaming passes over them:
 //
 //   P1  row maximum (the row mean is q . mean centroid, the minimum is bounded by
 //       -||q|| max ||c||, neither needs a pass);
@@ -34,7 +37,7 @@ constexpr int ST_NCH = kC / ST_CH;         // 16
 constexpr int ST_B = 64;                   // histogram buckets
 constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
-constexpr int ST_MAX_ITERS = 4;
+constexpr int ST_MAX_ITERS = 5;
 
 constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
 constexpr int OFF_A = OFF_CK + 1024 * 128;              // 128 rows x 128 B (first 64 B used)
@@ -43,14 +46,19 @@ constexpr int OFF_CAND = OFF_HIST;                      //   same bytes hold [12
 constexpr int OFF_SIZE = OFF_HIST + ST_B * 128 * 4;     // [2048] (cluster size << 12) + 1
 constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [4][128] per-group partial maxima, then [32] mean centroid
 constexpr int OFF_ROW = OFF_PART + 4 * 128 * 4 + 32 * 4;  // [12][128] per-row scalars
-constexpr int OFF_MISC = OFF_ROW + 13 * 128 * 4;        // union words, barriers, ...
+constexpr int ST_MAXSEG = 8;                            // query clusters one tile may span on the fast path
+constexpr int ST_MAXCQ = 2048;                          // prefix sums of the query-cluster sizes live in smem
+constexpr int OFF_UNION = OFF_ROW + 15 * 128 * 4;       // [ST_MAXSEG][64] segment bitmaps
+constexpr int OFF_PRE = OFF_UNION + ST_MAXSEG * 64 * 4; // [ST_MAXCQ + 1] first sorted row of every query cluster
+constexpr int OFF_MISC = OFF_PRE + (ST_MAXCQ + 4) * 4;  // barriers, segment tables, ...
 constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
 
 // RS_QUEUE + k: queued for the exact kernel; k says why (1 non-finite scores, 2 threshold not bracketed,
-// 3 too many candidates, 4 budget met above the window, 5 / 6 threshold outside the window, 7 walk ran dry)
+// 3 too many candidates, 4 budget met above the window, 5 / 6 threshold outside the window, 7 walk ran dry,
+// 8 the tile spans more query clusters than it has segment bitmaps)
 enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3 };
 // per-row scalar slots
-enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2 };
+enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2, R_CLU, R_SEG };
 
 __device__ __forceinline__ int key16_from_half(__half hv) {
   unsigned u = __half_as_ushort(hv);
@@ -64,7 +72,7 @@ __device__ __forceinline__ void wg_sync(int g) { asm volatile("bar.sync %0, 128;
 __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
     const int* __restrict__ kcounts, const int* __restrict__ qperm, const int* __restrict__ tile_sizes,
-    const int* __restrict__ ns_ptr, int* __restrict__ unip, int* __restrict__ rowcnt, int N, int CQ, int pin_tail,
+    const int* __restrict__ ns_ptr, int* __restrict__ unip, int* __restrict__ rowcnt, int N, int CQ,
     int* __restrict__ fixq, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -77,17 +85,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   float* sCbar = sPart + 4 * 128;
   float* sRowF = reinterpret_cast<float*>(sm + OFF_ROW);
   int* sRowI = reinterpret_cast<int*>(sm + OFF_ROW);
-  uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_MISC);              // [64]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_MISC + 256);          // [4]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 288);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 292);
-  int* sCmax = reinterpret_cast<int*>(sm + OFF_MISC + 296);                   // max ||cks||^2 as int bits
-  int* sOff = reinterpret_cast<int*>(sm + OFF_MISC + 300);                    // first sorted row of this cluster
+  uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_UNION);             // [ST_MAXSEG][64]
+  int* sPre = reinterpret_cast<int*>(sm + OFF_PRE);                           // [CQ + 1]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_MISC);                // [4]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 36);
+  int* sCmax = reinterpret_cast<int*>(sm + OFF_MISC + 40);                    // max ||cks||^2 as int bits
+  int* sScan = reinterpret_cast<int*>(sm + OFF_MISC + 64);                    // [16] scan scratch
+  int* sSegClu = reinterpret_cast<int*>(sm + OFF_MISC + 128);                 // [ST_MAXSEG] cluster of each segment
+  uint32_t* sSegMask = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 160);      // [4 warps][ST_MAXSEG] lanes of a segment
+  int* sNseg = reinterpret_cast<int*>(sm + OFF_MISC + 288);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = tid >> 7;            // column group: chunks g, g + 4, g + 8, g + 12
   const int r = tid & 127;           // row of the tile = TMEM lane
-  const int h = blockIdx.y, t = blockIdx.x;
+  const int h = blockIdx.y;
+  const int p0 = blockIdx.x * 128;                      // first sorted row of this tile
+  const int rows_here = min(128, N - p0);
   const __nv_bfloat16* ckh = cks + (size_t)h * kC * kR;
 
   if (warp == 0) {
@@ -97,11 +111,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   if (tid == 0) {
     *abort_flag = 0;
     *sCmax = 0;
-    *sOff = 0;
     for (int i = 0; i < 4; ++i) mbar_init(bars + i, 1);
     mbar_init_fence();
   }
-  if (tid < 64) sUnion[tid] = 0u;
+  sUnion[tid] = 0u;                                     // ST_MAXSEG * 64 == ST_THREADS words
   // all 2048 centroids: 16-byte chunk id -> centroid id >> 2, chunk id & 3
 #pragma unroll
   for (int i = 0; i < (kC * 4) / ST_THREADS; ++i) {
@@ -114,10 +127,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   if (tid < 32) sCbar[tid] = 0.f;
   __syncthreads();
   {
-    int part = 0;
-    for (int c = tid; c < t; c += ST_THREADS) part += tile_sizes[(size_t)h * CQ + c];
-    part = __reduce_add_sync(0xffffffffu, part);
-    if (lane == 0 && part) atomicAdd(sOff, part);
+    // exclusive prefix sums of the query-cluster sizes
+    int carry = 0;
+    for (int c0 = 0; c0 < CQ; c0 += ST_THREADS) {
+      const int c = c0 + tid;
+      const int v = c < CQ ? tile_sizes[(size_t)h * CQ + c] : 0;
+      const int inc = warp_incl_scan(v, lane);
+      if (lane == 31) sScan[warp] = inc;
+      __syncthreads();
+      int wbase = 0;
+      for (int w = 0; w < warp; ++w) wbase += sScan[w];
+      if (c < CQ) sPre[c] = carry + wbase + inc - v;
+      int tot = 0;
+      for (int w = 0; w < ST_THREADS / 32; ++w) tot += sScan[w];
+      carry += tot;
+      __syncthreads();
+    }
+    if (tid == 0) sPre[CQ] = carry;
   }
   cp_async_wait<0>();
   __syncthreads();
@@ -156,8 +182,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   const uint32_t tmem = *tmem_slot;
   const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, g * ST_CH);
   const int ns = *ns_ptr;
-  const int off = *sOff;
-  const int nrows = tile_sizes[(size_t)h * CQ + t];
   const float cmaxnorm = sqrtf(__int_as_float(*sCmax));
   constexpr uint32_t idesc = make_idesc_bf16(128, ST_CH, false, false);
   uint32_t ph = 0;
@@ -181,7 +205,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       if (!mbar_wait(bars + g, ph, abort_flag)) { dead = true; break; }
       ph ^= 1u;
       tc_fence_after();
-#pragma unroll
+#pragma unroll 1      // keeps each pass body at 32 columns of code; fully unrolled the kernel outgrows the I-cache
       for (int q = 0; q < 4; ++q) {
         uint32_t v[32];
         tmem_ld32(t_lane + q * 32, v);
@@ -193,23 +217,47 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     }
   };
 
-  for (int r0 = 0; r0 < nrows; r0 += 128) {
-    const int rows_here = min(128, nrows - r0);
-    // previous tile fully consumed; a group whose wait gave up takes the whole CTA out here, so every
-    // barrier below is reached by all threads or by none
-    if (__syncthreads_or(dead ? 1 : 0)) break;
+  {
     {
       const int ar = tid >> 2, ch = tid & 3;
       const bool valid = ar < rows_here;
-      const int orig = valid ? qperm[(size_t)h * N + off + r0 + ar] : 0;
+      const int orig = valid ? qperm[(size_t)h * N + p0 + ar] : 0;
       cp_async16(sA + sw128(ar, ch), QU + ((size_t)h * N + orig) * kR + ch * 8, valid ? 16u : 0u);
       cp_async_commit();
       if (ch == 0) sRowI[R_ORIG * 128 + ar] = orig;
+    }
+    if (g == 0) {
+      // query cluster of this sorted row: the last t with sPre[t] <= p (empty clusters are skipped)
+      int lo = 0, hi = CQ;                               // invariant: sPre[lo] <= p < sPre[hi]
+      const int p = p0 + (r < rows_here ? r : rows_here - 1);
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (sPre[mid] <= p) lo = mid; else hi = mid;
+      }
+      sRowI[R_CLU * 128 + r] = lo;
     }
     cp_async_wait<0>();
     fence_proxy_async();
     tc_fence_before();
     __syncthreads();
+    if (g == 0) {
+      // segment of the row = number of cluster changes before it
+      const int clu = sRowI[R_CLU * 128 + r];
+      const int flag = (r > 0 && sRowI[R_CLU * 128 + r - 1] != clu) ? 1 : 0;
+      const int inc = warp_incl_scan(flag, lane);
+      if (lane == 31) sScan[warp] = inc;
+      wg_sync(0);
+      int seg = inc;
+      for (int w = 0; w < warp; ++w) seg += sScan[w];
+      sRowI[R_SEG * 128 + r] = seg;
+      if (seg < ST_MAXSEG && (flag || r == 0)) sSegClu[seg] = clu;
+      if (r == 127) *sNseg = seg + 1 < ST_MAXSEG ? seg + 1 : ST_MAXSEG;
+#pragma unroll
+      for (int k = 0; k < ST_MAXSEG; ++k) {
+        const uint32_t m = __ballot_sync(0xffffffffu, seg == k && r < rows_here);
+        if (lane == 0) sSegMask[warp * ST_MAXSEG + k] = m;
+      }
+    }
     if (g == 0) {
       float qn = 0.f, mean = 0.f;
 #pragma unroll
@@ -228,8 +276,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       const float bound = sqrtf(qn) * cmaxnorm;
       sRowF[R_EPS * 128 + r] = 6.103515625e-05f * bound + 1.0e-30f;
       sRowF[R_LO * 128 + r] = mean;
-      sRowF[R_MIN * 128 + r] = -bound;
-      sRowI[R_STATE * 128 + r] = r < rows_here ? RS_SEARCH : RS_DONE;
+      sRowI[R_STATE * 128 + r] =
+          r < rows_here ? (sRowI[R_SEG * 128 + r] < ST_MAXSEG ? RS_SEARCH : RS_QUEUE + 8) : RS_DONE;
       sRowI[R_CUM * 128 + r] = 0;
       sRowI[R_NCAND * 128 + r] = 0;
       sRowI[R_SIZEA * 128 + r] = 0;
@@ -254,9 +302,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       const float M = fmaxf(fmaxf(sPart[r], sPart[128 + r]), fmaxf(sPart[256 + r], sPart[384 + r]));
       const float mean = sRowF[R_LO * 128 + r];
       const bool finite = fabsf(M) < INFINITY && fabsf(mean) < INFINITY;
-      const float lo = fminf(mean, M);
+      // First range: the top part of [mean, max].  For small budgets the threshold sits in the upper tail
+      // (1.5 % of a bell-shaped score distribution is ~0.4 (max - mean) below the maximum), and every
+      // cluster inside the range costs a shared-memory atomic.  If the threshold turns out to lie lower
+      // the search continues over [mean, lo) and then [-bound, mean).
+      const float frac = (long long)ns * 20 <= (long long)N ? 0.6f : 1.0f;
+      const float lo = fminf(M, M - frac * (M - fminf(mean, M)));
       sRowF[R_HI * 128 + r] = M;
       sRowF[R_LO * 128 + r] = lo;
+      sRowF[R_MIN * 128 + r] = fminf(mean, lo);       // next lower end if the threshold is below lo
       sRowF[R_INV * 128 + r] = M > lo ? (float)ST_B / (M - lo) : 0.f;
       if (!finite) sRowI[R_STATE * 128 + r] = RS_QUEUE + 1;
     }
@@ -299,13 +353,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         }
         const float w = (hi - lo) * (1.0f / ST_B);
         if (bstar < 0) {
-          // the threshold lies below this range: continue from its lower end down to the row minimum
+          // the threshold lies below this range: continue from its lower end down to the next floor
+          // (first the row mean, then the lower bound -||q|| max ||c|| of any score)
           const float mn = sRowF[R_MIN * 128 + r];
           if (lo > mn && it + 1 < ST_MAX_ITERS) {
             sRowI[R_CUM * 128 + r] = cum;
             sRowF[R_HI * 128 + r] = lo;
             sRowF[R_LO * 128 + r] = mn;
             sRowF[R_INV * 128 + r] = (float)ST_B / (lo - mn);
+            sRowF[R_MIN * 128 + r] = -sRowF[R_EPS * 128 + r] * 16384.0f - 1.0f;      // below -bound
             searching = 1;
           } else {
             sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
@@ -339,6 +395,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       const float thrA = act ? sRowF[R_THRA * 128 + r] : INFINITY;
       const float thrW = act ? sRowF[R_THRW * 128 + r] : INFINITY;
       int sumA = 0;      // packed: (sizes << 12) + count
+      const int nseg = *sNseg;
+      const uint32_t* segmask = sSegMask + (warp & 3) * ST_MAXSEG;
+      // segment of this warp's rows if they all share one (the common case), else -1
+      int one_seg = -1;
+      for (int k = 0; k < nseg; ++k)
+        if (segmask[k] != 0u) one_seg = (one_seg == -1) ? k : -2;
       stream([&](int cbase, const uint32_t(&v)[32]) {
         uint32_t wbits = 0u;
 #pragma unroll
@@ -354,10 +416,25 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
               const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
               if (slot < ST_CAP) sCand[r * ST_CAP + slot] = (uint32_t)(cbase + j4 + e);
             }
-            wbits |= __ballot_sync(0xffffffffu, above) ? (1u << (j4 + e)) : 0u;
+            wbits |= above ? (1u << (j4 + e)) : 0u;
           }
         }
-        if (lane == 0 && wbits && (sUnion[cbase >> 5] & wbits) != wbits) atomicOr(&sUnion[cbase >> 5], wbits);
+        // clusters some row of this warp takes outright -> the bitmap of the rows' segment(s)
+        const uint32_t any = __reduce_or_sync(0xffffffffu, wbits);
+        if (any) {
+          if (one_seg >= 0) {
+            uint32_t* w = sUnion + one_seg * 64 + (cbase >> 5);
+            if (lane == 0 && (*w & any) != any) atomicOr(w, any);
+          } else {
+#pragma unroll 1
+            for (int k = 0; k < nseg; ++k) {
+              const uint32_t mine = (segmask[k] >> lane) & 1u ? wbits : 0u;
+              const uint32_t segbits = __reduce_or_sync(0xffffffffu, mine);
+              uint32_t* w = sUnion + k * 64 + (cbase >> 5);
+              if (lane == 0 && segbits && (*w & segbits) != segbits) atomicOr(w, segbits);
+            }
+          }
+        }
       });
       if (sumA) atomicAdd(&sRowI[R_SIZEA * 128 + r], sumA >> 12);
     }
@@ -399,6 +476,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       int st = sRowI[R_STATE * 128 + r];
       const int n = sRowI[R_NCAND * 128 + r];
       const int orig = sRowI[R_ORIG * 128 + r];
+      uint32_t* myUnion = sUnion + (sRowI[R_SEG * 128 + r] & (ST_MAXSEG - 1)) * 64;
       if (st == RS_COLLECT) {
         int running = sRowI[R_SIZEA * 128 + r];
         // Independent of how the window was found, the result is exact iff the exact threshold key lies
@@ -436,7 +514,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             used |= 1ull << best;
             const int sz = sSizeP[bidx] >> 12;
             const uint32_t bit = 1u << (bidx & 31);
-            if (!(sUnion[bidx >> 5] & bit)) atomicOr(&sUnion[bidx >> 5], bit);
+            if (!(myUnion[bidx >> 5] & bit)) atomicOr(&myUnion[bidx >> 5], bit);
             if (running + sz >= ns) rc = running + sz;
             running += sz;
           }
@@ -448,20 +526,27 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         int* qh = fixq + (size_t)h * (2 * (size_t)N + 1);
         const int slot = atomicAdd(qh, 1);
         qh[1 + 2 * slot] = orig;
-        qh[2 + 2 * slot] = t | ((st - RS_QUEUE) << 24);      // the reason rides in the top byte
+        qh[2 + 2 * slot] = sRowI[R_CLU * 128 + r] | ((st - RS_QUEUE) << 24);      // the reason rides in the top byte
       }
     }
   }
   __syncthreads();
-  if (tid < 64) {
-    uint32_t w = sUnion[tid];
-    if (pin_tail > 0 && tid == 63) w |= 0x80000000u;
-    unip[((size_t)h * CQ + t) * 64 + tid] = (int)w;
+  {
+    // segment bitmaps -> the (zero-initialised) bitmaps of their query clusters
+    const int k = tid >> 6, w = tid & 63;
+    const uint32_t bits = sUnion[tid];
+    if (k < *sNseg && bits) atomicOr(reinterpret_cast<unsigned*>(unip) + ((size_t)h * CQ + sSegClu[k]) * 64 + w, bits);
   }
   if (*abort_flag && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// pin_tail: every query cluster executes the reserved last key cluster
+__global__ void pin_bit_kernel(int* __restrict__ unip, int rows) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) atomicOr(reinterpret_cast<unsigned*>(unip) + (size_t)i * 64 + 63, 0x80000000u);
 }
 
 size_t select_ws_bytes(int H, int N) { return (size_t)H * (2 * (size_t)N + 1) * sizeof(int); }
@@ -479,13 +564,19 @@ extern "C" int t2t_score_select_union(const void* QU, const void* cks, const voi
   if (!QU || !cks || !kcounts || !qperm || !tile_sizes || !ns || !unip || !rowcnt || !ws) return T2T_ERR_ARG;
   if (H <= 0 || N <= 0 || CQ <= 0 || N >= (1 << 19)) return T2T_ERR_ARG;
   if (ws_bytes < select_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
+  if (CQ > ST_MAXCQ)      // the prefix sums of the query clusters would not fit: all-exact path
+    return t2t_score_select_union_exact(QU, cks, kcounts, qperm, tile_sizes, ns, unip, rowcnt, H, N, CQ, pin_tail,
+                                        st);
   int* fixq = (int*)ws;
-  if (cudaMemsetAsync(fixq, 0, select_ws_bytes(H, N), st) != cudaSuccess) return T2T_ERR_CUDA;
+  if (cudaMemsetAsync(fixq, 0, select_ws_bytes(H, N), st) != cudaSuccess ||
+      cudaMemsetAsync(unip, 0, (size_t)H * CQ * 64 * sizeof(int), st) != cudaSuccess)
+    return T2T_ERR_CUDA;
   if (cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
-  select_tc_kernel<<<dim3(CQ, H), ST_THREADS, ST_SMEM, st>>>(
+  select_tc_kernel<<<dim3(cdiv(N, 128), H), ST_THREADS, ST_SMEM, st>>>(
       (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const int*)qperm,
-      (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, pin_tail, fixq, d_status);
+      (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, fixq, d_status);
+  if (pin_tail > 0) pin_bit_kernel<<<cdiv(H * CQ, 256), 256, 0, st>>>((int*)unip, H * CQ);
   if (cudaGetLastError() != cudaSuccess) return T2T_ERR_CUDA;
   return launch_select_fix((const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, ns, (int*)unip,
                            (int*)rowcnt, H, N, CQ, fixq, st);
