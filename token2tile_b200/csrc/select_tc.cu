@@ -32,8 +32,8 @@
 namespace t2t {
 
 constexpr int ST_THREADS = 512;
-constexpr int ST_CH = 128;                 // centroids per MMA chunk
-constexpr int ST_NCH = kC / ST_CH;         // 16
+constexpr int ST_CH = 64;                  // centroids per MMA chunk
+constexpr int ST_NCH = kC / ST_CH;         // 32: eight per column group, double-buffered in TMEM
 constexpr int ST_B = 64;                   // histogram buckets
 constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
@@ -87,17 +87,17 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   int* sRowI = reinterpret_cast<int*>(sm + OFF_ROW);
   uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_UNION);             // [ST_MAXSEG][64]
   int* sPre = reinterpret_cast<int*>(sm + OFF_PRE);                           // [CQ + 1]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_MISC);                // [4]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 32);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 36);
-  int* sCmax = reinterpret_cast<int*>(sm + OFF_MISC + 40);                    // max ||cks||^2 as int bits
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + OFF_MISC);                // [4 groups][2 buffers]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 320);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + OFF_MISC + 324);
+  int* sCmax = reinterpret_cast<int*>(sm + OFF_MISC + 328);                    // max ||cks||^2 as int bits
   int* sScan = reinterpret_cast<int*>(sm + OFF_MISC + 64);                    // [16] scan scratch
   int* sSegClu = reinterpret_cast<int*>(sm + OFF_MISC + 128);                 // [ST_MAXSEG] cluster of each segment
   uint32_t* sSegMask = reinterpret_cast<uint32_t*>(sm + OFF_MISC + 160);      // [4 warps][ST_MAXSEG] lanes of a segment
   int* sNseg = reinterpret_cast<int*>(sm + OFF_MISC + 288);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int g = tid >> 7;            // column group: chunks g, g + 4, g + 8, g + 12
+  const int g = tid >> 7;            // column group: chunks g, g + 4, g + 8, ...
   const int r = tid & 127;           // row of the tile = TMEM lane
   const int h = blockIdx.y;
   const int p0 = blockIdx.x * 128;                      // first sorted row of this tile
@@ -111,7 +111,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   if (tid == 0) {
     *abort_flag = 0;
     *sCmax = 0;
-    for (int i = 0; i < 4; ++i) mbar_init(bars + i, 1);
+    for (int i = 0; i < 8; ++i) mbar_init(bars + i, 1);
     mbar_init_fence();
   }
   sUnion[tid] = 0u;                                     // ST_MAXSEG * 64 == ST_THREADS words
@@ -180,41 +180,49 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, g * ST_CH);
+  const uint32_t t_lane = tmem_addr(tmem, (warp & 3) * 32, g * 2 * ST_CH);      // two buffers of ST_CH columns
   const int ns = *ns_ptr;
   const float cmaxnorm = sqrtf(__int_as_float(*sCmax));
   constexpr uint32_t idesc = make_idesc_bf16(128, ST_CH, false, false);
-  uint32_t ph = 0;
+  uint32_t ph0 = 0, ph1 = 0;        // phases of this group's two buffer barriers
   bool dead = false;
 
-  // Streams this group's four chunks through its TMEM buffer; body(cbase, v)
-  // sees 32 consecutive approximate scores of this thread's row.
-  auto stream = [&](auto&& body) {
-#pragma unroll 1
-    for (int i = 0; i < ST_NCH / 4 && !dead; ++i) {
-      const int cc = g + 4 * i;
-      if (r == 0) {
-        tc_fence_after();
+  // Streams this group's eight chunks through its two TMEM buffers: the MMA of
+  // chunk i + 1 runs while chunk i is scanned.  body(cbase, v) sees 32
+  // consecutive approximate scores of this thread's row.
+  auto issue = [&](int i) {        // called by the group's first thread
+    const int cc = g + 4 * i, b = i & 1;
+    tc_fence_after();
 #pragma unroll
-        for (int s2 = 0; s2 < 2; ++s2)
-          umma_ss(tmem + g * ST_CH, make_sdesc(sA + s2 * 32, 16, 1024),
-                  make_sdesc(sCk + (cc & 7) * (ST_CH * 128) + (cc >> 3) * 64 + s2 * 32, 16, 1024), idesc,
-                  s2 > 0 ? 1u : 0u);
-        umma_commit(bars + g);
-      }
-      if (!mbar_wait(bars + g, ph, abort_flag)) { dead = true; break; }
-      ph ^= 1u;
+    for (int s2 = 0; s2 < 2; ++s2)
+      umma_ss(tmem + g * 2 * ST_CH + b * ST_CH, make_sdesc(sA + s2 * 32, 16, 1024),
+              make_sdesc(sCk + (cc & 15) * (ST_CH * 128) + (cc >> 4) * 64 + s2 * 32, 16, 1024), idesc,
+              s2 > 0 ? 1u : 0u);
+    umma_commit(bars + g * 2 + b);
+  };
+  auto stream = [&](auto&& body) {
+    if (dead) return;
+    if (r == 0) issue(0);
+#pragma unroll 1
+    for (int i = 0; i < ST_NCH / 4; ++i) {
+      const int cc = g + 4 * i, b = i & 1;
+      // every warp of the group has finished reading the other buffer (chunk i - 1): refill it
+      tc_fence_before();
+      wg_sync(g);
+      if (r == 0 && i + 1 < ST_NCH / 4) issue(i + 1);
+      if (!mbar_wait(bars + g * 2 + b, b ? ph1 : ph0, abort_flag)) { dead = true; break; }
+      if (b) ph1 ^= 1u; else ph0 ^= 1u;
       tc_fence_after();
 #pragma unroll 1      // keeps each pass body at 32 columns of code; fully unrolled the kernel outgrows the I-cache
-      for (int q = 0; q < 4; ++q) {
+      for (int q = 0; q < ST_CH / 32; ++q) {
         uint32_t v[32];
-        tmem_ld32(t_lane + q * 32, v);
+        tmem_ld32(t_lane + b * ST_CH + q * 32, v);
         tmem_wait_ld();
         body(cc * ST_CH + q * 32, v);
       }
-      tc_fence_before();
-      wg_sync(g);          // all four warps of the group are done with the buffer
     }
+    tc_fence_before();
+    wg_sync(g);
   };
 
   {

@@ -11,8 +11,8 @@
 //   residual :  S = QU cks^T (128 queries x 128 centroids, K = 32)
 //               T += P sumv (128 x 128, K = 128 centroids)
 //
-// A query row is one TMEM lane, owned by one thread (residual) or by two threads
-// that split its columns (attention), so row maxima and sums need no shuffles.  K/V rows of a union are contiguous runs in the cluster-major
+// One thread owns one query row (TMEM lane), so row maxima and sums need no
+// shuffles.  K/V rows of a union are contiguous runs in the cluster-major
 // copies kp/vp and are gathered with 16-byte cp.async into 128-byte-swizzled
 // tiles.  Two CTAs share an SM (256 TMEM columns each) so that the softmax of
 // one overlaps the MMAs and loads of the other.  Every mbarrier wait is
@@ -210,15 +210,11 @@ __device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
 // ---------------------------------------------------------------------------
 // exact attention over the unions
 // ---------------------------------------------------------------------------
-// 256 threads: two threads per query row.  Thread (half, row) owns TMEM lane
-// `row` and the 64 key columns [64 half, 64 half + 64) of every S tile, and the
-// 64 output columns [64 half, 64 half + 64) of O.
-constexpr int AT_THREADS = 256;
 constexpr int AT_TILE = KT * kD * 2;   // 32 KB
-constexpr int AT_SMEM_INTS = 2 * KT + 2 * MAX_RUNS + 8 + 32 + 4 * QT;
+constexpr int AT_SMEM_INTS = 2 * KT + 2 * MAX_RUNS + 8 + 32;
 constexpr int AT_SMEM = 3 * AT_TILE + 64 + AT_SMEM_INTS * 4 + 1024;
 
-__global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
+__global__ void __launch_bounds__(128, 2) attn_kernel(
     const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp,
     const uint32_t* __restrict__ ub, const int* __restrict__ qperm, __nv_bfloat16* __restrict__ attn_out,
     float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ, int* __restrict__ status) {
@@ -234,11 +230,9 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
   int* sRunStart = sInt + 2 * KT;       // [MAX_RUNS]
   int* sRunCum = sRunStart + MAX_RUNS;  // [MAX_RUNS + 1]
   int* sMisc = sRunCum + MAX_RUNS + 8;  // [0] task, [1] runs; scan scratch from [8]
-  float* sHalf = reinterpret_cast<float*>(sMisc + 32);   // [2 buffers][2 halves][QT] row maxima / sums exchanged
 
   const PlanView pv = plan_view(plan, H, N, CQ);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int half = tid >> 7, row = tid & 127;
 
   if (warp == 0) {
     tmem_alloc(tmem_slot, 256);
@@ -255,18 +249,15 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-  const uint32_t tS_mine = tS + lane_base + half * 64;    // my 64 score columns
-  const uint32_t tP_mine = tS + lane_base + half * 32;    // my 32 packed P columns
-  const uint32_t tO_mine = tO + lane_base + half * 64;    // my 64 output columns
+  const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
   uint32_t phS = 0, phO = 0;
   const int numTasks = pv.counters[0];
   const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
 
-  const int ld_ch = tid & 15, ld_r0 = tid >> 4;          // 16 rows per pass, 8 passes per tile
-  const uint32_t ld_blk = (ld_ch >> 3) * (KT * 128);     // 64-column block of this thread's chunk
+  const int ld_ch = tid & 15, ld_r0 = tid >> 4;
+  const uint32_t ld_blk = (ld_ch >> 3) * (KT * 128);   // 64-column block of this thread's chunk
 
   while (true) {
     __syncthreads();
@@ -280,16 +271,16 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
     const size_t rowbase = (size_t)h * N + qs;
 
     if (kvlen == 0) {   // empty union: O = 0, lse = -inf
-      for (int i = tid; i < qrows * 16; i += AT_THREADS)
+      for (int i = tid; i < qrows * 16; i += 128)
         reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
-      for (int r = tid; r < qrows; r += AT_THREADS) attn_lse[rowbase + r] = -INFINITY;
+      for (int r = tid; r < qrows; r += 128) attn_lse[rowbase + r] = -INFINITY;
       continue;
     }
 
     // ---- Q tile, gathered through qperm --------------------------------------
 #pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int r = ld_r0 + 16 * u;
+    for (int u = 0; u < 16; ++u) {
+      const int r = ld_r0 + 8 * u;
       const bool valid = r < qrows;
       const int orig = qperm[rowbase + (valid ? r : 0)];
       cp_async16(sQ + ld_blk + sw128(r, ld_ch & 7), q + ((size_t)h * N + orig) * kD + ld_ch * 8,
@@ -297,44 +288,44 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
     }
     cp_async_commit();
 
-    // ---- runs of selected, non-empty key clusters (8 clusters per thread) ------
+    // ---- runs of selected, non-empty key clusters -----------------------------
     {
       const int* koh = pv.k_off + (size_t)h * (kC + 1);
       const uint32_t* ubr = ub + ((size_t)h * CQ + qc) * (kC / 32);
-      const int c0 = tid * 8;
-      const uint32_t bw = (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFu;
-      int offs[9];
-#pragma unroll
-      for (int j = 0; j < 9; ++j) offs[j] = koh[c0 + j];
+      const int c0 = tid * 16;
+      const uint32_t bw = (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu;
+      const int base0 = koh[c0];
       bool pne0 = false;
-      if (c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && offs[0] > koh[c0 - 1];
+      if (c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
+      int offs[17];
+      offs[0] = base0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
       int cnt = 0, sz = 0;
       {
         bool pne = pne0;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 16; ++j) {
           const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
           if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
           pne = cne;
         }
       }
-      int* ws = sMisc + 8;     // [8] run counts, [8] token counts per warp
+      // 128-thread exclusive scans of (cnt, sz)
+      int* ws = sMisc + 8;
       const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
-      if (lane == 31) { ws[warp] = ic; ws[8 + warp] = is; }
+      if (lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
       __syncthreads();
-      int kbase = ic - cnt, pbase = is - sz, totc = 0;
-#pragma unroll
-      for (int w = 0; w < 8; ++w) {
-        if (w < warp) { kbase += ws[w]; pbase += ws[8 + w]; }
-        totc += ws[w];
-      }
+      int kbase = ic - cnt, pbase = is - sz;
+      for (int w = 0; w < warp; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
+      const int totc = ws[0] + ws[1] + ws[2] + ws[3];
       if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
         if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
       } else {
         bool pne = pne0;
         int k = kbase, p = pbase;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 16; ++j) {
           const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
           if (cne) {
             if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
@@ -342,7 +333,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
           }
           pne = cne;
         }
-        if (tid == AT_THREADS - 1) { sRunCum[k] = p; sMisc[1] = totc; }
+        if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
       }
       __syncthreads();
       if (*abort_flag) break;
@@ -362,20 +353,22 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
     auto load_tile = [&](uint32_t dst, const __nv_bfloat16* src, const int* gidx) {
       const __nv_bfloat16* sb = src + (size_t)h * N * kD + ld_ch * 8;
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        const int r = ld_r0 + 16 * u;
+      for (int u = 0; u < 16; ++u) {
+        const int r = ld_r0 + 8 * u;
         const int g = gidx[r];
         cp_async16(dst + ld_blk + sw128(r, ld_ch & 7), sb + (size_t)(g < 0 ? 0 : g) * kD, g < 0 ? 0u : 16u);
       }
       cp_async_commit();
     };
 
-    sGidx[tid] = key_row(tid);          // tiles 0 and 1: 256 key slots, one per thread
+    sGidx[tid] = key_row(tid);
+    sGidx[KT + tid] = key_row(KT + tid);
     __syncthreads();
     load_tile(sK, kp, sGidx);
 
-    float m_ref = -INFINITY;            // maximum (log2 domain) the stored P and O are relative to
-    float l_part = 0.f;                 // denominator over this thread's columns
+    RowState rs;
+    rs.m = -INFINITY;
+    rs.l = 0.f;
     bool dead = false;
 
     for (int t = 0; t < ntiles; ++t) {
@@ -407,67 +400,59 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
       const bool more = t + 1 < ntiles;
       if (more) load_tile(sK, kp, gnxt);
 
-      // ---- softmax over this thread's 64 columns ---------------------------------
-      float s[64];
+      // ---- softmax of this thread's row --------------------------------------
+      float s[KT];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(tS_mine + c * 32, v);
+        tmem_ld32(tS_lane + c * 32, v);
         tmem_wait_ld();
 #pragma unroll
         for (int j = 0; j < 32; ++j) s[c * 32 + j] = __uint_as_float(v[j]);
       }
-      const int valid = kvlen - t * KT - half * 64;    // valid columns among mine
-      if (valid < 64) {
+      const int valid = kvlen - t * KT;
+      if (valid < KT) {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) if (j >= valid) s[j] = -INFINITY;
+        for (int j = 0; j < KT; ++j) if (j >= valid) s[j] = -INFINITY;
       }
-      float mx4[4] = {s[0], s[1], s[2], s[3]};
+      float mx4[4] = {s[0], s[1], s[2], s[3]};      // independent chains: a single one is 127 dependent ops
 #pragma unroll
-      for (int j = 4; j < 64; j += 4) {
+      for (int j = 4; j < KT; j += 4) {
         mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
         mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
       }
-      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
-      float* xch = sHalf + (t & 1) * 2 * QT;
-      xch[half * QT + row] = mx;
-      __syncthreads();
-      mx = fmaxf(mx, xch[(half ^ 1) * QT + row]);      // maximum over all 128 columns of the row
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
       if (t == 0) {
-        m_ref = mx;
+        rs.m = mx;
       } else {
-        const bool grow = mx > m_ref + kLazy;
+        const bool grow = mx > rs.m + kLazy;
         if (__any_sync(0xffffffffu, grow)) {
-          const float mnew = grow ? mx : m_ref;
-          const float alpha = ex2_approx(m_ref - mnew);
-#pragma unroll
-          for (int c = 0; c < 2; ++c) {
-            uint32_t v[32];
-            tmem_ld32(tO_mine + c * 32, v);
-            tmem_wait_ld();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
-            tmem_st32(tO_mine + c * 32, v);
-          }
-          l_part *= alpha;
-          m_ref = mnew;
+          const float mnew = grow ? mx : rs.m;
+          const float alpha = ex2_approx(rs.m - mnew);
+          rescale_rows(tO_lane, alpha);
+          rs.l *= alpha;
+          rs.m = mnew;
         }
       }
-      const float nm = -m_ref;
+      const float nm = -rs.m;
       float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[KT / 2];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {          // 32 scores -> 16 packed columns at a time
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = ex2_approx(fmaf(s[c * 32 + 2 * j], sc, nm));
-          const float p1 = ex2_approx(fmaf(s[c * 32 + 2 * j + 1], sc, nm));
-          ls4[j & 3] += p0 + p1;
-          pk[j] = pack_bf2(p0, p1);
-        }
-        tmem_st16(tP_mine + c * 16, pk);
+      for (int j = 0; j < KT / 2; ++j) {
+        const float p0 = ex2_approx(fmaf(s[2 * j], sc, nm));
+        const float p1 = ex2_approx(fmaf(s[2 * j + 1], sc, nm));
+        ls4[j & 3] += p0 + p1;
+        pk[j] = pack_bf2(p0, p1);
       }
-      l_part += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+      rs.l += lsum;
+      {
+        uint32_t lo[32], hi[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { lo[j] = pk[j]; hi[j] = pk[32 + j]; }
+        tmem_st32(tS_lane, lo);
+        tmem_st32(tS_lane + 32, hi);
+      }
       tmem_wait_st();
       if (more) cp_async_wait<1>(); else cp_async_wait<0>();   // V(t) has landed
       fence_proxy_async();
@@ -483,7 +468,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
         umma_commit(bars + 1);
       }
       // rows of tile t + 2 replace those of tile t
-      if (tid < KT && t + 2 < ntiles) sGidx[(t & 1) * KT + tid] = key_row((t + 2) * KT + tid);
+      if (t + 2 < ntiles) sGidx[(t & 1) * KT + tid] = key_row((t + 2) * KT + tid);
     }
     if (!dead) {
       if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
@@ -492,17 +477,13 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
     if (dead) break;
     tc_fence_after();
     {
-      float* xch = sHalf + (ntiles & 1) * 2 * QT;
-      xch[half * QT + row] = l_part;
-      __syncthreads();
-      const float l = l_part + xch[(half ^ 1) * QT + row];
-      const float inv = 1.0f / l;
-      const bool wr = row < qrows;
-      uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + row) * kD + half * 64);
+      const float inv = 1.0f / rs.l;
+      const bool wr = tid < qrows;
+      uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + tid) * kD);
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
-        tmem_ld32(tO_mine + c * 32, v);
+        tmem_ld32(tO_lane + c * 32, v);
         tmem_wait_ld();
         if (wr) {
 #pragma unroll
@@ -516,7 +497,7 @@ __global__ void __launch_bounds__(AT_THREADS, 2) attn_kernel(
           }
         }
       }
-      if (wr && half == 0) attn_lse[rowbase + row] = (m_ref + log2f(l)) * 0.6931471805599453f;
+      if (wr) attn_lse[rowbase + tid] = (rs.m + log2f(rs.l)) * 0.6931471805599453f;
     }
     tc_fence_before();
   }
@@ -661,14 +642,15 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
       for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
     }
     const uint32_t mw[4] = {mw4.x, mw4.y, mw4.z, mw4.w};
-    float mx = -INFINITY;
+    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
     for (int i = 0; i < TL_C; ++i) {
       // the score is rounded to fp16 exactly as the selection saw it
       const float g = __half2float(__float2half_rn(s[i])) * LOG2E;
       s[i] = ((mw[i >> 5] >> (i & 31)) & 1u) ? -INFINITY : g;
-      mx = fmaxf(mx, s[i]);
+      mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
     }
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
     const bool grow = mx > m + kLazy || (m == -INFINITY && mx > -INFINITY);
     if (__any_sync(0xffffffffu, grow)) {
       const float mnew = grow ? mx : m;
@@ -678,16 +660,16 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
       m = mnew;
     }
     const float nm = (m == -INFINITY) ? 0.f : -m;
-    float ps = 0.f;
+    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
     uint32_t pk[TL_C / 2];
 #pragma unroll
     for (int i = 0; i < TL_C / 2; ++i) {
       const float p0 = ex2_approx(s[2 * i] + nm);
       const float p1 = ex2_approx(s[2 * i + 1] + nm);
-      ps = fmaf(p0, sCnt[2 * i], ps);
-      ps = fmaf(p1, sCnt[2 * i + 1], ps);
+      ps4[i & 3] = fmaf(p1, sCnt[2 * i + 1], fmaf(p0, sCnt[2 * i], ps4[i & 3]));
       pk[i] = pack_bf2(p0, p1);
     }
+    const float ps = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
     phi += ps;
     {
       uint32_t lo[32], hi[32];
@@ -805,7 +787,7 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
-  attn_kernel<<<2 * sms, AT_THREADS, AT_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kp,
+  attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kp,
                                              (const __nv_bfloat16*)vp, (const uint32_t*)unip, (const int*)qperm,
                                              attn_out, attn_lse, plan, H, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
