@@ -293,8 +293,13 @@ def run_ours(args, rank, world, local_rank):
     roofline = None
     if t_attn > 0:
         ach = flops / (t_attn * 1e-3) / 1e12
+        # DRAM bytes of one launch: 256.4 MB (dram__bytes_read + write) in the ncu capture of the 8-head 480p
+        # case (profiles/attn_kernel_480p_8heads.md), scaled by the rows processed (q, kp, vp read once and the
+        # exact output written once: traffic is proportional to H * N)
+        traffic = 256.4e6 * (Hl * float(N)) / (8 * 32760.0)
         roofline = {"kernel": "attn_kernel", "bound": "tensor", "achieved": ach, "peak": pk["tf"],
-                    "unit": "TFLOP/s", "frac": ach / pk["tf"], "traffic": None, "peak_source": pk["src"] +
+                    "unit": "TFLOP/s", "frac": ach / pk["tf"], "traffic": traffic,
+                    "traffic_source": "ncu 480p x 8 heads capture scaled by rows", "peak_source": pk["src"] +
                     " (sustained bf16 GEMM)", "flops_per_launch": flops, "ms_per_launch": t_attn,
                     "executed_pair_fraction": pairs / (Hl * float(N) * N)}
     B = 2

@@ -145,3 +145,37 @@ def test_argument_errors(small_case):
     bad[0, 0, 0] = float("nan")
     with pytest.raises(RuntimeError):
         op.init_state(bad, q)
+
+
+def test_head_sharding_is_bitwise_neutral(small_case):
+    """Heads never interact: running each head in its own operator (what a rank
+    of a head-parallel layout does) gives the bits of the joint run."""
+    from token2tile_b200 import MaskedStepDeploy
+    c = small_case
+    H, N, CQ = c["H"], c["N"], c["CQ"]
+    q, k, v = (c[n].to(DEV) for n in "qkv")
+    joint = MaskedStepDeploy(H, N, CQ, s_frac=0.05)
+    out = joint.step(q, k, v, {n: t.to(DEV) for n, t in c["state"].items()}).clone()
+    torch.cuda.synchronize()
+    for h in range(H):
+        part = MaskedStepDeploy(1, N, CQ, s_frac=0.05)
+        st = {n: t[h:h + 1].contiguous().to(DEV) for n, t in c["state"].items()}
+        o = part.step(q[h:h + 1].contiguous(), k[h:h + 1].contiguous(), v[h:h + 1].contiguous(), st)
+        torch.cuda.synchronize()
+        assert part.device_status() == 0
+        assert torch.equal(o.view(torch.int16), out[h:h + 1].view(torch.int16))
+        assert torch.equal(part.last_structure["unip"], joint.last_structure["unip"][h:h + 1])
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_devices_give_the_same_bits(small_case):
+    from token2tile_b200 import MaskedStepDeploy
+    c = small_case
+    outs = []
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            op = MaskedStepDeploy(c["H"], c["N"], c["CQ"], s_frac=0.05, device=dev)
+            o = op.step(*(c[n].to(dev) for n in "qkv"), {n: t.to(dev) for n, t in c["state"].items()})
+            torch.cuda.synchronize(dev)
+            outs.append(o.cpu())
+    assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
