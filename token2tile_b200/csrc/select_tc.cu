@@ -38,17 +38,18 @@ constexpr int ST_B = 64;                   // histogram buckets
 constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
 constexpr int ST_MAX_ITERS = 5;
+constexpr int ST_STRAGGLERS = 8;           // this few unsettled rows of a tile go to the exact kernel instead of another pass
 
 constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
 constexpr int OFF_A = OFF_CK + 1024 * 128;              // 128 rows x 128 B (first 64 B used)
 constexpr int OFF_HIST = OFF_A + 128 * 128;             // [ST_B][128] packed (size << 12 | count); after P2 the
 constexpr int OFF_CAND = OFF_HIST;                      //   same bytes hold [128][ST_CAP] cluster | key << 16
 constexpr int OFF_SIZE = OFF_HIST + ST_B * 128 * 4;     // [2048] (cluster size << 12) + 1
-constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [4][128] per-group partial maxima, then [32] mean centroid
-constexpr int OFF_ROW = OFF_PART + 4 * 128 * 4 + 32 * 4;  // [12][128] per-row scalars
+constexpr int OFF_PART = OFF_SIZE + kC * 4;             // [3][4][128] per-group partial max / sum / sum of squares
+constexpr int OFF_ROW = OFF_PART + 12 * 128 * 4;        // [17][128] per-row scalars
 constexpr int ST_MAXSEG = 8;                            // query clusters one tile may span on the fast path
 constexpr int ST_MAXCQ = 2048;                          // prefix sums of the query-cluster sizes live in smem
-constexpr int OFF_UNION = OFF_ROW + 15 * 128 * 4;       // [ST_MAXSEG][64] segment bitmaps
+constexpr int OFF_UNION = OFF_ROW + 17 * 128 * 4;       // [ST_MAXSEG][64] segment bitmaps
 constexpr int OFF_PRE = OFF_UNION + ST_MAXSEG * 64 * 4; // [ST_MAXCQ + 1] first sorted row of every query cluster
 constexpr int OFF_MISC = OFF_PRE + (ST_MAXCQ + 4) * 4;  // barriers, segment tables, ...
 constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
@@ -58,7 +59,7 @@ constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
 // 8 the tile spans more query clusters than it has segment bitmaps)
 enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3 };
 // per-row scalar slots
-enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2, R_CLU, R_SEG };
+enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2, R_CLU, R_SEG, R_OVF, R_MAX };
 
 __device__ __forceinline__ int key16_from_half(__half hv) {
   unsigned u = __half_as_ushort(hv);
@@ -82,7 +83,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   uint32_t* sCand = reinterpret_cast<uint32_t*>(sm + OFF_CAND);
   int* sSizeP = reinterpret_cast<int*>(sm + OFF_SIZE);
   float* sPart = reinterpret_cast<float*>(sm + OFF_PART);
-  float* sCbar = sPart + 4 * 128;
   float* sRowF = reinterpret_cast<float*>(sm + OFF_ROW);
   int* sRowI = reinterpret_cast<int*>(sm + OFF_ROW);
   uint32_t* sUnion = reinterpret_cast<uint32_t*>(sm + OFF_UNION);             // [ST_MAXSEG][64]
@@ -124,7 +124,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   }
   cp_async_commit();
   for (int c = tid; c < kC; c += ST_THREADS) sSizeP[c] = (kcounts[(size_t)h * kC + c] << 12) + 1;
-  if (tid < 32) sCbar[tid] = 0.f;
   __syncthreads();
   {
     // exclusive prefix sums of the query-cluster sizes
@@ -167,13 +166,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
     if (lane == 0) atomicMax(sCmax, __float_as_int(mx));
-    // mean centroid (only places the histogram range, so the summation order does not matter)
-    const int d = tid & 31, sub = tid >> 5;
-    float acc = 0.f;
-    for (int c = sub * 128; c < sub * 128 + 128; ++c)
-      acc += bf_to_f(*reinterpret_cast<const __nv_bfloat16*>(sm + OFF_CK + sw128(c & 1023, (c >> 10) * 4 + (d >> 3)) +
-                                                            (d & 7) * 2));
-    atomicAdd(&sCbar[d], acc * (1.0f / kC));
   }
   fence_proxy_async();
   tc_fence_before();
@@ -267,23 +259,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       }
     }
     if (g == 0) {
-      float qn = 0.f, mean = 0.f;
+      float qn = 0.f;
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
         const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, q4));
         const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float lo = bf_lo(ws[e]), hi = bf_hi(ws[e]);
-          qn = fmaf(lo, lo, qn);
-          qn = fmaf(hi, hi, qn);
-          mean = fmaf(lo, sCbar[q4 * 8 + e * 2], mean);
-          mean = fmaf(hi, sCbar[q4 * 8 + e * 2 + 1], mean);
+          qn = fmaf(bf_lo(ws[e]), bf_lo(ws[e]), qn);
+          qn = fmaf(bf_hi(ws[e]), bf_hi(ws[e]), qn);
         }
       }
       const float bound = sqrtf(qn) * cmaxnorm;
       sRowF[R_EPS * 128 + r] = 6.103515625e-05f * bound + 1.0e-30f;
-      sRowF[R_LO * 128 + r] = mean;
+      sRowF[R_MIN * 128 + r] = -bound - 1.0f;
       sRowI[R_STATE * 128 + r] =
           r < rows_here ? (sRowI[R_SEG * 128 + r] < ST_MAXSEG ? RS_SEARCH : RS_QUEUE + 8) : RS_DONE;
       sRowI[R_CUM * 128 + r] = 0;
@@ -291,35 +280,51 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       sRowI[R_SIZEA * 128 + r] = 0;
     }
 
-    // ---- P1: row maximum --------------------------------------------------------
+    // ---- P1: row maximum, mean and standard deviation of the approximate scores ----------
     {
-      float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+      float mx0 = -INFINITY, mx1 = -INFINITY, s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
       stream([&](int, const uint32_t(&v)[32]) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          mx0 = fmaxf(mx0, __uint_as_float(v[j]));
-          mx1 = fmaxf(mx1, __uint_as_float(v[j + 1]));
-          mx2 = fmaxf(mx2, __uint_as_float(v[j + 2]));
-          mx3 = fmaxf(mx3, __uint_as_float(v[j + 3]));
+        for (int j = 0; j < 32; j += 2) {
+          const float a = __uint_as_float(v[j]), b2 = __uint_as_float(v[j + 1]);
+          mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b2);
+          s1a += a; s1b += b2;
+          s2a = fmaf(a, a, s2a); s2b = fmaf(b2, b2, s2b);
         }
       });
-      sPart[g * 128 + r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      sPart[(0 * 4 + g) * 128 + r] = fmaxf(mx0, mx1);
+      sPart[(1 * 4 + g) * 128 + r] = s1a + s1b;
+      sPart[(2 * 4 + g) * 128 + r] = s2a + s2b;
     }
     __syncthreads();
     if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
-      const float M = fmaxf(fmaxf(sPart[r], sPart[128 + r]), fmaxf(sPart[256 + r], sPart[384 + r]));
-      const float mean = sRowF[R_LO * 128 + r];
-      const bool finite = fabsf(M) < INFINITY && fabsf(mean) < INFINITY;
-      // First range: the top part of [mean, max].  For small budgets the threshold sits in the upper tail
-      // (1.5 % of a bell-shaped score distribution is ~0.4 (max - mean) below the maximum), and every
-      // cluster inside the range costs a shared-memory atomic.  If the threshold turns out to lie lower
-      // the search continues over [mean, lo) and then [-bound, mean).
-      const float frac = (long long)ns * 20 <= (long long)N ? 0.6f : 1.0f;
-      const float lo = fminf(M, M - frac * (M - fminf(mean, M)));
-      sRowF[R_HI * 128 + r] = M;
+      float M = -INFINITY, s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int gg = 0; gg < 4; ++gg) {
+        M = fmaxf(M, sPart[(0 * 4 + gg) * 128 + r]);
+        s1 += sPart[(1 * 4 + gg) * 128 + r];
+        s2 += sPart[(2 * 4 + gg) * 128 + r];
+      }
+      const float mean = s1 * (1.0f / kC);
+      const float sd = sqrtf(fmaxf(s2 * (1.0f / kC) - mean * mean, 1.0e-20f));
+      const bool finite = fabsf(M) < INFINITY && fabsf(s2) < INFINITY;
+      // First range: 2.5 standard deviations around the score a fraction ns / N of a bell-shaped
+      // distribution would exceed (inverse normal tail, Abramowitz-Stegun 26.2.23).  Everything above the
+      // range is counted in an overflow bucket.  The range only has to be a good guess: the search continues
+      // above or below it when the running token count says so.
+      const float f = fminf(0.5f, fmaxf((float)ns / (float)N, 1.0e-6f));
+      const float tt = sqrtf(-2.0f * __logf(f));
+      const float z = tt - (2.515517f + tt * (0.802853f + tt * 0.010328f)) /
+                               (1.0f + tt * (1.432788f + tt * (0.189269f + tt * 0.001308f)));
+      float hi = mean + (z + 1.25f) * sd;
+      const int ovf = hi < M ? 1 : 0;
+      hi = ovf ? hi : M;
+      const float lo = fminf(mean + (z - 1.25f) * sd, hi);
+      sRowF[R_MAX * 128 + r] = M;
+      sRowF[R_HI * 128 + r] = hi;
       sRowF[R_LO * 128 + r] = lo;
-      sRowF[R_MIN * 128 + r] = fminf(mean, lo);       // next lower end if the threshold is below lo
-      sRowF[R_INV * 128 + r] = M > lo ? (float)ST_B / (M - lo) : 0.f;
+      sRowI[R_OVF * 128 + r] = ovf;
+      sRowF[R_INV * 128 + r] = hi > lo ? (float)(ST_B - ovf) / (hi - lo) : 0.f;
       if (!finite) sRowI[R_STATE * 128 + r] = RS_QUEUE + 1;
     }
 
@@ -333,6 +338,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         const bool act = sRowI[R_STATE * 128 + r] == RS_SEARCH;
         const float hi = act ? sRowF[R_HI * 128 + r] : -INFINITY;
         const float inv = act ? sRowF[R_INV * 128 + r] : 1.0f;
+        // with an overflow bucket, bucket 0 takes every score above hi and the range starts at bucket 1
+        const int ovf = act ? sRowI[R_OVF * 128 + r] : 0;
+        const int bmin = ovf - 1;
         int* hist_r = sHist + r;
         stream([&](int cbase, const uint32_t(&v)[32]) {
 #pragma unroll
@@ -341,7 +349,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             const int pp[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int b = __float2int_rd((hi - __uint_as_float(v[j4 + e])) * inv);
+              const int b = max(__float2int_rd((hi - __uint_as_float(v[j4 + e])) * inv) + ovf, bmin);
               if ((unsigned)b < (unsigned)ST_B) atomicAdd(hist_r + b * 128, pp[e]);
             }
           }
@@ -352,14 +360,33 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
         const float hi = sRowF[R_HI * 128 + r], lo = sRowF[R_LO * 128 + r];
         const float eps = sRowF[R_EPS * 128 + r];
+        const int ovf = sRowI[R_OVF * 128 + r];
         int cum = sRowI[R_CUM * 128 + r];
         int bstar = -1, cnt = 0;
-        for (int b = 0; b < ST_B; ++b) {
+        bool above = false;                       // the budget is met inside the overflow bucket
+        if (ovf) {
+          const int p = sHist[r];
+          if (cum + (p >> 12) >= ns) above = true; else cum += p >> 12;
+        }
+        for (int b = ovf; b < ST_B && !above; ++b) {
           const int p = sHist[b * 128 + r];
-          if (cum + (p >> 12) >= ns) { bstar = b; cnt = p & 4095; break; }
+          if (cum + (p >> 12) >= ns) { bstar = b - ovf; cnt = p & 4095; break; }
           cum += p >> 12;
         }
-        const float w = (hi - lo) * (1.0f / ST_B);
+        const float w = (hi - lo) / (float)(ST_B - ovf);
+        if (above) {
+          // continue between hi and the row maximum (nothing has been added to cum)
+          if (it + 1 < ST_MAX_ITERS) {
+            const float M = sRowF[R_MAX * 128 + r];
+            sRowF[R_LO * 128 + r] = hi;
+            sRowF[R_HI * 128 + r] = M;
+            sRowI[R_OVF * 128 + r] = 0;
+            sRowF[R_INV * 128 + r] = M > hi ? (float)ST_B / (M - hi) : 0.f;
+            searching = 1;
+          } else {
+            sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
+          }
+        } else
         if (bstar < 0) {
           // the threshold lies below this range: continue from its lower end down to the next floor
           // (first the row mean, then the lower bound -||q|| max ||c|| of any score)
@@ -369,7 +396,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             sRowF[R_HI * 128 + r] = lo;
             sRowF[R_LO * 128 + r] = mn;
             sRowF[R_INV * 128 + r] = (float)ST_B / (lo - mn);
-            sRowF[R_MIN * 128 + r] = -sRowF[R_EPS * 128 + r] * 16384.0f - 1.0f;      // below -bound
+            sRowI[R_OVF * 128 + r] = 0;
+            sRowF[R_MIN * 128 + r] = lo;               // no further floor: a second miss goes to the exact kernel
             searching = 1;
           } else {
             sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
@@ -383,6 +411,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             sRowF[R_HI * 128 + r] = x_hi;
             sRowF[R_LO * 128 + r] = x_lo;
             sRowF[R_INV * 128 + r] = (float)ST_B / (x_hi - x_lo);
+            sRowI[R_OVF * 128 + r] = 0;
             searching = 1;
           } else {
             sRowF[R_THRA * 128 + r] = x_hi + e2;
@@ -392,7 +421,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
           }
         }
       }
-      if (!__syncthreads_or(searching)) break;
+      const int unsettled = __syncthreads_count(searching);
+      if (unsettled == 0) break;
+      if (unsettled <= ST_STRAGGLERS) {          // cheaper to hand a few rows to the exact kernel than to run a pass
+        if (searching) sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
+        break;
+      }
     }
     if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) sRowI[R_STATE * 128 + r] = RS_QUEUE + 2;
     __syncthreads();
