@@ -28,7 +28,9 @@ constexpr int MAX_RUNS = 1024;   // runs of selected clusters in one union
 constexpr int PLAN_SORT_MAX = 2048;
 constexpr int PLAN_HDR = 8;      // counters: [0] tasks, [1] attention cursor, [2..3] executed pairs (lo, hi)
 
-__host__ __device__ inline size_t plan_task_offset(int H) { return ((size_t)H * (kC + 1) + PLAN_HDR + 3) & ~(size_t)3; }
+// the counters start on a 16-byte boundary (the pair count is a 64-bit atomic), the tasks follow them
+__host__ __device__ inline size_t plan_counter_offset(int H) { return ((size_t)H * (kC + 1) + 3) & ~(size_t)3; }
+__host__ __device__ inline size_t plan_task_offset(int H) { return plan_counter_offset(H) + PLAN_HDR; }
 __host__ __device__ inline size_t plan_max_tasks(int H, int N, int CQ) { return (size_t)H * (CQ + cdiv(N, QT) + 1); }
 
 struct PlanView {
@@ -40,7 +42,7 @@ struct PlanView {
 __host__ __device__ inline PlanView plan_view(int* plan, int H, int N, int CQ) {
   PlanView v;
   v.k_off = plan;
-  v.counters = plan + (size_t)H * (kC + 1);
+  v.counters = plan + plan_counter_offset(H);
   v.tasks = reinterpret_cast<int4*>(plan + plan_task_offset(H));
   v.kv_lens = plan + plan_task_offset(H) + 4 * plan_max_tasks(H, N, CQ);
   return v;
