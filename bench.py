@@ -35,6 +35,7 @@ sys.path.insert(0, str(ROOT))
 WORKLOAD = dict(name="wan2.1-14b-720p-self-attention-layer", H=40, grid="720p", N=75600, CQ=512, D=128,
                 s_frac=0.015)
 KERNELS_REBUILD = 2 + 21 + 2 + 1 + 2 + 2  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), select+fix, gather, plan, attention+merge
+KERNELS_REUSE = 1 + 1 + 3 + 2   # project q, gather k, value stats, attention + merge
 METRIC = "t2t_attn_ms_per_layer"
 UNIT = "ms/layer"
 
@@ -119,6 +120,12 @@ def dense_attention_ms(q, k, v):
         from flash_attn import flash_attn_func
         qf, kf, vf = (t.transpose(0, 1).unsqueeze(0).contiguous() for t in (q, k, v))
         cands["flash_attn"] = lambda: flash_attn_func(qf, kf, vf)
+    except Exception:      # noqa: BLE001 - optional library
+        pass
+    try:
+        import flashinfer
+        qi, ki, vi = (t.transpose(0, 1).contiguous() for t in (q, k, v))
+        cands["flashinfer"] = lambda: flashinfer.single_prefill_with_kv_cache(qi, ki, vi, causal=False)
     except Exception:      # noqa: BLE001 - optional library
         pass
     for name, run in cands.items():
@@ -350,6 +357,148 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------
+# full transformer step (40 blocks, Ulysses sequence parallelism at N > 1)
+# ---------------------------------------------------------------------------
+
+def run_dit(args, rank, world, local_rank):
+    """One denoising step = both CFG branches through all blocks.  The timed
+    steps cover one refresh period of the structure (mask_refresh = 4): the
+    first rebuilds in branch 0, everything else reuses."""
+    import torch.distributed as dist
+    from token2tile_b200 import dit_step as D
+    from token2tile_b200 import t2t_attn as B
+    from token2tile_b200.synth import GRIDS
+
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+        B.set_ulysses_world_size(world)
+    shape = D.WAN_14B
+    grid = GRIDS[args.grid or "720p"]
+    N = grid[0] * grid[1] * grid[2]
+    CQ = {75600: 512, 32760: 256}.get(N, max(32, N // 128))
+    ns = max(1, int(0.015 * N))
+    if N % world or shape.heads % world:
+        raise SystemExit(f"{N} tokens / {shape.heads} heads do not split over {world} ranks")
+    B.set_backend_config({"t2t_fast_init": True})
+
+    class DenseImpl:
+        def __init__(self, num_heads, head_size, causal, softmax_scale, prefix=""):
+            self.dense = B.DenseAttention(num_heads, head_size, softmax_scale)
+
+        def forward(self, q, k, v, meta):
+            return self.dense.forward(q, k, v)
+
+    nblocks = args.blocks or shape.blocks
+    model = D.DiTStep(shape, device=dev, seed=0, group=group, blocks=nblocks,
+                      make_attn=DenseImpl if args.dense_attention else None)
+    # residual stream: a locality mixture in the model width (512 centres, blocks of 1x4x4 tokens)
+    g = torch.Generator(device=dev).manual_seed(1234)
+    T, Y, X = grid
+    t = torch.arange(T, device=dev)[:, None, None].expand(T, Y, X)
+    y = torch.arange(Y, device=dev)[None, :, None].expand(T, Y, X)
+    x = torch.arange(X, device=dev)[None, None, :].expand(T, Y, X)
+    by, bx = (Y + 3) // 4, (X + 3) // 4
+    block = ((t * by + y // 4) * bx + x // 4).reshape(N)
+    cen = torch.randn(512, shape.dim, generator=g, device=dev)
+    pick = torch.randint(0, 512, (T * by * bx,), generator=g, device=dev)
+    n = N // world
+    rows = slice(rank * n, (rank + 1) * n)
+    noise = torch.randn(N, shape.dim, generator=g, device=dev)[rows]
+    x_dev = (cen[pick[block[rows]]] + 0.3 * noise).to(torch.bfloat16).contiguous()
+    del noise
+    text = torch.randn(shape.text_len, shape.text_dim, generator=g, device=dev).to(torch.bfloat16)
+    hx = x_dev.cpu().pin_memory()
+    hout = torch.empty_like(hx).pin_memory()
+
+    build = B.T2TAttentionMetadataBuilder().build
+    cache = B.T2TRequestCache()
+
+    def meta(step):
+        return build(step, 50, cache, profile_name="manual", ns_base=ns, dense_prefix_steps=0, cq=CQ, ck=2048,
+                     step_profile=(1.0,) * 4, layer_profile=(1.0,) * 6, cfg_mult=(1.0, 1.0), mask_refresh=4,
+                     cfg_reuse=True)
+
+    counter = [0]
+
+    def denoise_step(host=False):
+        step = counter[0]
+        counter[0] += 1
+        m = meta(step)
+        if host:
+            x_dev.copy_(hx, non_blocking=True)
+        for branch in range(2):
+            out = model.forward(x_dev, text, 999.0 - 20 * step, m)
+        if host:
+            hout.copy_(out, non_blocking=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def maxr(v):
+        if world == 1:
+            return v
+        tt = torch.tensor([v], device=dev, dtype=torch.float64)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    warm = max(4, (args.warmup + 3) // 4 * 4)       # whole refresh periods, so the timed steps start with a rebuild
+    for _ in range(warm):
+        denoise_step()
+    barrier()
+    steps = args.steps
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    rebuilds = sum(1 for s_ in range(counter[0], counter[0] + steps) if s_ % 4 == 0)   # branch-0 calls that rebuild
+    ms = time_events(denoise_step, steps)
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    ms_step = maxr(ms / steps)
+    counter[0] = (counter[0] + 3) // 4 * 4
+    denoise_step(host=True)
+    barrier()
+    counter[0] = (counter[0] + 3) // 4 * 4
+    e2e_ms = maxr(time_events(lambda: denoise_step(host=True), steps) / steps)
+    barrier()
+    if not args.dense_attention:
+        for rt in B._RUNTIMES.values():
+            assert rt.deploy.device_status() == 0, "a device wait timed out"
+    if rank == 0:
+        pk = peaks()
+        gemm_flops = 2 * D.flops_per_step(D.DiTShape(blocks=nblocks), N) / world      # two branches, this rank's tokens
+        line = {
+            "metric": "dit_denoising_step_ms", "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": steps,
+            "warmup": warm, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "wan2.1-14b-shaped-dit-step-" + (args.grid or "720p"), "blocks": nblocks,
+                       "dim": shape.dim, "heads": shape.heads, "ffn": shape.ffn, "N": N, "text_tokens": shape.text_len,
+                       "cfg_branches_per_step": 2, "rebuild_steps_in_timed_region": rebuilds, "self_attention": "dense" if args.dense_attention else
+                       f"token2tile ns={ns} CQ={CQ} mask_refresh=4 cfg_reuse", "parallelism": f"ulysses x{world}",
+                       "weights_GB": model.weight_bytes() / 1e9,
+                       "all_to_all_bytes_per_rank_per_block": D.all_to_all_bytes_per_block(shape, N, world),
+                       "l2": "activations (0.77 GB per tensor) exceed L2; no flush"},
+            "roofline": {"kernel": "dense GEMMs of the step (cuBLAS)", "bound": "tensor",
+                         "achieved": gemm_flops / (ms_step * 1e-3) / 1e12, "peak": pk["tf"], "unit": "TFLOP/s",
+                         "frac": gemm_flops / (ms_step * 1e-3) / 1e12 / pk["tf"], "traffic": None,
+                         "note": "GEMM FLOPs only over the whole step time: a lower bound on utilisation"},
+            "cpu_baseline": None,
+            "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": hx.numel() * 2,
+                    "d2h_bytes_per_step": hout.numel() * 2},
+            "gpu_launches": None if args.dense_attention else
+            nblocks * (rebuilds * KERNELS_REBUILD + (2 * steps - rebuilds) * KERNELS_REUSE),
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -360,6 +509,10 @@ def main():
     ap.add_argument("--heads", type=int, default=0, help="override the head count (profiling cases)")
     ap.add_argument("--grid", default="", choices=["", "cpu", "480p", "720p"], help="override the latent grid")
     ap.add_argument("--light", action="store_true", help="timed steps and stage times only")
+    ap.add_argument("--workload", default="layer", choices=["layer", "dit_step"],
+                    help="layer: one attention layer (the headline metric); dit_step: a full transformer step")
+    ap.add_argument("--blocks", type=int, default=0, help="dit_step: number of blocks (default 40)")
+    ap.add_argument("--dense-attention", action="store_true", help="dit_step: dense self-attention instead")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -369,7 +522,10 @@ def main():
     else:
         if args.warmup < 3:
             args.warmup = 3
-        run_ours(args, rank, world, local_rank)
+        if args.workload == "dit_step":
+            run_dit(args, rank, world, local_rank)
+        else:
+            run_ours(args, rank, world, local_rank)
 
 
 if __name__ == "__main__":
