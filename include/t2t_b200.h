@@ -192,6 +192,15 @@ int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, int* d_info, 
 int t2t_umma_selftest(const void* A, const void* B, const void* V, float* S_out, float* O_out,
                       int* d_status, cudaStream_t stream);
 
+/* TMA row-gather self-test: gathers the 128 rows `gidx[0..127]` of the bf16
+ * matrix src [rows, 128] into one SWIZZLE_128B shared-memory tile (two blocks of
+ * 64 columns, 128-byte rows, 16-byte chunk c of row r stored at chunk
+ * c ^ (r & 7)) and copies the tile's 32 KB to `out` unchanged.  Same tensor map
+ * and instruction form as the attention kernel's K / V tile loads.  No
+ * counterpart in the reference. */
+int t2t_gather4_selftest(const void* src, int rows, const int* gidx, void* out, int* d_status,
+                         cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -43,6 +43,7 @@ SIGNATURES = {
     "t2t_tile_attn_merge": (_I, [_P] * 10 + [_I, _I, _I, _P, _S, _P, _P]),
     "t2t_tile_attn_plan_info": (_I, [_P, _I, _I, _I, _P, _P]),
     "t2t_umma_selftest": (_I, [_P, _P, _P, _P, _P, _P, _P]),
+    "t2t_gather4_selftest": (_I, [_P, _I, _P, _P, _P, _P]),
 }
 
 

@@ -69,6 +69,10 @@ __device__ __forceinline__ void mbar_init_fence() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival that also announces `bytes` of asynchronous copies completing on this barrier.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -94,6 +98,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   *abort_flag = 1;
   return false;
+}
+
+// ---- TMA row gather ----------------------------------------------------------
+// Four rows of a 2D tensor (row indices r0..r3, starting at column `col`) land as
+// four consecutive rows of a SWIZZLE_128B shared-memory tile: 4 x (box columns)
+// elements per instruction, completion counted in bytes on `bar`.  `map` is a
+// tensor map whose box is (box columns) x 1 row; `col` x element size must be
+// a multiple of 16 bytes.  No multicast: the destination is this CTA's own
+// shared memory.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const void* map, int col, int r0, int r1, int r2, int r3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4, %5, %6}], [%7];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(r0), "r"(r1), "r"(r2), "r"(r3), "r"(smem_u32(bar))
+      : "memory");
 }
 
 // ---- tcgen05 / TMEM ---------------------------------------------------------

@@ -20,4 +20,9 @@ int launch_assign(const __nv_bfloat16* X, const __nv_bfloat16* cen, int* labels,
 int launch_select_fix(const __nv_bfloat16* QU, const __nv_bfloat16* cks, const int* kcounts, const int* ns,
                       int* unip, int* rowcnt, int H, int N, int CQ, const int* fixq, cudaStream_t st);
 
+// Tensor map (128 bytes, written to map_out) over the bf16 matrix base [rows, 128]
+// with a 64-column x 1-row box and 128-byte swizzle, for tma_gather4 (tma_rows.cu).
+// False when the driver entry point is missing or the encoding is refused.
+bool make_row_gather_map(void* map_out, const void* base, uint64_t rows);
+
 }  // namespace t2t
