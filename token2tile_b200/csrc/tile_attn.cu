@@ -17,7 +17,10 @@
 // tiles.  Two CTAs share an SM (256 TMEM columns each) so that the softmax of
 // one overlaps the MMAs and loads of the other.  Every mbarrier wait is
 // bounded; on a timeout the CTA raises a status word and leaves.
+#include <cuda.h>
+
 #include "common.cuh"
+#include "internal.h"
 #include "t2t_b200.h"
 
 namespace t2t {
@@ -213,23 +216,26 @@ __device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
 // exact attention over the unions
 // ---------------------------------------------------------------------------
 constexpr int AT_TILE = KT * kD * 2;   // 32 KB
-constexpr int AT_SMEM_INTS = 2 * KT + 2 * MAX_RUNS + 8 + 32;
+constexpr int AT_SMEM_INTS = 5 * KT + 2 * MAX_RUNS + 8 + 32;
 constexpr int AT_SMEM = 3 * AT_TILE + 64 + AT_SMEM_INTS * 4 + 1024;
 
 __global__ void __launch_bounds__(128, 2) attn_kernel(
-    const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kp, const __nv_bfloat16* __restrict__ vp,
-    const uint32_t* __restrict__ ub, const int* __restrict__ qperm, __nv_bfloat16* __restrict__ attn_out,
-    float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ, int* __restrict__ status) {
+    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+    const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
+    __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
+    int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
   const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 2 * AT_TILE;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 3 * AT_TILE);          // [0] S ready, [1] O ready
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + 3 * AT_TILE + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + 3 * AT_TILE + 32);
+  // [0] S ready, [1] O ready, [2] K tile landed, [3] V tile landed, [4] Q tile landed
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 3 * AT_TILE);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + 3 * AT_TILE + 40);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + 3 * AT_TILE + 48);
   int* sInt = reinterpret_cast<int*>(sm + 3 * AT_TILE + 64);
-  int* sGidx = sInt;                    // [2][KT] row of kp/vp for every key slot of a tile, -1 past the end
-  int* sRunStart = sInt + 2 * KT;       // [MAX_RUNS]
+  int* sGidx = sInt;                    // [4][KT] row of kp/vp (all heads) for every key slot of a tile
+  int* sQidx = sInt + 4 * KT;           // [KT] row of q for every query slot of the task
+  int* sRunStart = sInt + 5 * KT;       // [MAX_RUNS]
   int* sRunCum = sRunStart + MAX_RUNS;  // [MAX_RUNS + 1]
   int* sMisc = sRunCum + MAX_RUNS + 8;  // [0] task, [1] runs; scan scratch from [8]
 
@@ -242,8 +248,7 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
   }
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(bars + 0, 1);
-    mbar_init(bars + 1, 1);
+    for (int i = 0; i < 5; ++i) mbar_init(bars + i, 1);
     mbar_init_fence();
   }
   tc_fence_before();
@@ -251,6 +256,7 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
+  uint32_t phK = 0, phV = 0, phQ = 0;      // used by thread 0 only
   const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
   uint32_t phS = 0, phO = 0;
   const int numTasks = pv.counters[0];
@@ -258,8 +264,15 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
 
-  const int ld_ch = tid & 15, ld_r0 = tid >> 4;
-  const uint32_t ld_blk = (ld_ch >> 3) * (KT * 128);   // 64-column block of this thread's chunk
+  // Tile loads: 64 TMA instructions per 128-row tile, each four rows of one 64-column block.  Threads
+  // 0..63 issue the K tile's, threads 64..127 the V (or Q) tile's.
+  const int ld_i = tid & 63, ld_blk = ld_i >> 5, ld_grp = ld_i & 31;
+  const uint32_t ld_off = ld_blk * (KT * 128) + ld_grp * 512;
+  auto gather_tile = [&](uint32_t dst, const CUtensorMap* map, const int* rows, uint64_t* bar) {
+    if (ld_i == 0) mbar_arrive_expect_tx(bar, AT_TILE);
+    const int4 r = reinterpret_cast<const int4*>(rows)[ld_grp];
+    tma_gather4(dst + ld_off, map, ld_blk * 64, r.x, r.y, r.z, r.w, bar);
+  };
 
   while (true) {
     __syncthreads();
@@ -279,16 +292,8 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
       continue;
     }
 
-    // ---- Q tile, gathered through qperm --------------------------------------
-#pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      const int r = ld_r0 + 8 * u;
-      const bool valid = r < qrows;
-      const int orig = qperm[rowbase + (valid ? r : 0)];
-      cp_async16(sQ + ld_blk + sw128(r, ld_ch & 7), q + ((size_t)h * N + orig) * kD + ld_ch * 8,
-                 valid ? 16u : 0u);
-    }
-    cp_async_commit();
+    // ---- rows of the Q tile, through qperm (slots past the task repeat its first row) --------
+    sQidx[tid] = h * N + qperm[rowbase + (tid < qrows ? tid : 0)];
 
     // ---- runs of selected, non-empty key clusters -----------------------------
     {
@@ -343,30 +348,40 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
 
-    auto key_row = [&](int p) -> int {   // kp/vp row of the p-th token of the union
-      if (p >= kvlen) return -1;
+    auto key_row = [&](int p) -> int {   // kp/vp row (all heads) of the p-th token of the union
+      if (p >= kvlen) return h * N;     // slots past the union read a real row; their scores are masked
       int lo = 0, hi = nruns - 1;
       while (lo < hi) {
         const int mid = (lo + hi + 1) >> 1;
         if (sRunCum[mid] <= p) lo = mid; else hi = mid - 1;
       }
-      return sRunStart[lo] + p - sRunCum[lo];
+      return h * N + sRunStart[lo] + p - sRunCum[lo];
     };
-    auto load_tile = [&](uint32_t dst, const __nv_bfloat16* src, const int* gidx) {
-      const __nv_bfloat16* sb = src + (size_t)h * N * kD + ld_ch * 8;
-#pragma unroll
-      for (int u = 0; u < 16; ++u) {
-        const int r = ld_r0 + 8 * u;
-        const int g = gidx[r];
-        cp_async16(dst + ld_blk + sw128(r, ld_ch & 7), sb + (size_t)(g < 0 ? 0 : g) * kD, g < 0 ? 0u : 16u);
-      }
-      cp_async_commit();
-    };
-
     sGidx[tid] = key_row(tid);
     sGidx[KT + tid] = key_row(KT + tid);
+    sGidx[2 * KT + tid] = key_row(2 * KT + tid);
     __syncthreads();
-    load_tile(sK, kp, sGidx);
+    if (tid < 64) gather_tile(sK, &mapK, sGidx, bars + 2);
+    else gather_tile(sQ, &mapQ, sQidx, bars + 4);
+    auto issue_qk = [&]() {      // thread 0: S = Q K^T once the K tile has landed
+      if (!mbar_wait(bars + 2, phK, abort_flag)) return;
+      phK ^= 1u;
+      tc_fence_after();
+#pragma unroll
+      for (int s = 0; s < 8; ++s) {
+        const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
+        const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
+        umma_ss(tS, ad, bd, idescQK, s > 0 ? 1u : 0u);
+      }
+      umma_commit(bars + 0);
+    };
+    if (tid == 0) {
+      tc_fence_after();
+      if (mbar_wait(bars + 4, phQ, abort_flag)) {
+        phQ ^= 1u;
+        issue_qk();
+      }
+    }
 
     RowState rs;
     rs.m = -INFINITY;
@@ -374,22 +389,8 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     bool dead = false;
 
     for (int t = 0; t < ntiles; ++t) {
-      const int* gcur = sGidx + (t & 1) * KT;
-      const int* gnxt = sGidx + ((t + 1) & 1) * KT;
-      cp_async_wait<0>();          // Q (first tile) and K(t) have landed
-      fence_proxy_async();
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-#pragma unroll
-        for (int s = 0; s < 8; ++s) {
-          const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
-          const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
-          umma_ss(tS, ad, bd, idescQK, s > 0 ? 1u : 0u);
-        }
-        umma_commit(bars + 0);
-      }
+      const int* gcur = sGidx + (t & 3) * KT;
+      const int* gnxt = sGidx + ((t + 1) & 3) * KT;
       if (!mbar_wait(bars + 0, phS, abort_flag)) { dead = true; break; }
       phS ^= 1u;
       if (t > 0) {
@@ -398,19 +399,26 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
       }
       tc_fence_after();
       // K tile and V tile buffers are free now
-      load_tile(sV, vp, gcur);
       const bool more = t + 1 < ntiles;
-      if (more) load_tile(sK, kp, gnxt);
+      if (tid >= 64) gather_tile(sV, &mapV, gcur, bars + 3);
+      else if (more) gather_tile(sK, &mapK, gnxt, bars + 2);
 
       // ---- softmax of this thread's row --------------------------------------
       float s[KT];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tS_lane + c * 32, v);
+      {
+        uint32_t v0[32], v1[32], v2[32], v3[32];
+        tmem_ld32(tS_lane, v0);
+        tmem_ld32(tS_lane + 32, v1);
+        tmem_ld32(tS_lane + 64, v2);
+        tmem_ld32(tS_lane + 96, v3);
         tmem_wait_ld();
 #pragma unroll
-        for (int j = 0; j < 32; ++j) s[c * 32 + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 32; ++j) {
+          s[j] = __uint_as_float(v0[j]);
+          s[32 + j] = __uint_as_float(v1[j]);
+          s[64 + j] = __uint_as_float(v2[j]);
+          s[96 + j] = __uint_as_float(v3[j]);
+        }
       }
       const int valid = kvlen - t * KT;
       if (valid < KT) {
@@ -456,21 +464,24 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
         tmem_st32(tS_lane + 32, hi);
       }
       tmem_wait_st();
-      if (more) cp_async_wait<1>(); else cp_async_wait<0>();   // V(t) has landed
-      fence_proxy_async();
       tc_fence_before();
       __syncthreads();
       if (tid == 0) {
         tc_fence_after();
+        if (mbar_wait(bars + 3, phV, abort_flag)) {      // V(t) has landed
+          phV ^= 1u;
 #pragma unroll
-        for (int s8 = 0; s8 < 8; ++s8) {
-          const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
-          umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+          for (int s8 = 0; s8 < 8; ++s8) {
+            const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
+            umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+          }
+          umma_commit(bars + 1);
+          if (more) issue_qk();
         }
-        umma_commit(bars + 1);
       }
-      // rows of tile t + 2 replace those of tile t
-      if (t + 2 < ntiles) sGidx[(t & 1) * KT + tid] = key_row((t + 2) * KT + tid);
+      // Rows of tile t + 3, while the tensor core works.  Their buffer was last read in iteration t - 1,
+      // and the barrier of iteration t + 1 orders this write before its first reader (iteration t + 2).
+      if (t + 3 < ntiles) sGidx[((t + 3) & 3) * KT + tid] = key_row((t + 3) * KT + tid);
     }
     if (!dead) {
       if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
@@ -503,8 +514,11 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     }
     tc_fence_before();
   }
-  if (*abort_flag && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
-  cp_async_wait<0>();
+  if (*abort_flag) {
+    if (tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+    // a wait gave up: let tile copies still in flight land before the shared memory is released
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
@@ -789,9 +803,14 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
-  attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)kp,
-                                             (const __nv_bfloat16*)vp, (const uint32_t*)unip, (const int*)qperm,
-                                             attn_out, attn_lse, plan, H, N, CQ, d_status);
+  // tensor maps over q, kp, vp as [H * N, 128] matrices: the kernel fetches tile rows four at a time
+  CUtensorMap mq, mk, mv;
+  const uint64_t rows = (uint64_t)H * (uint64_t)N;
+  if (!make_row_gather_map(&mq, q, rows) || !make_row_gather_map(&mk, kp, rows) ||
+      !make_row_gather_map(&mv, vp, rows))
+    return T2T_ERR_CUDA;
+  attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
+                                             plan, H, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
 
