@@ -25,11 +25,13 @@
 
 namespace t2t {
 
-constexpr int QT = 128;          // query rows per task
+constexpr int QT = 128;          // query rows per tensor-core tile (one thread per row)
+constexpr int TASK_ROWS = 256;   // query rows per task: tasks above QT rows run as two tiles sharing one K/V stream
 constexpr int KT = 128;          // keys per tile
 constexpr int MAX_RUNS = 1024;   // runs of selected clusters in one union
 constexpr int PLAN_SORT_MAX = 2048;
-constexpr int PLAN_HDR = 8;      // counters: [0] tasks, [1] attention cursor, [2..3] executed pairs (lo, hi)
+constexpr int PLAN_HDR = 8;      // counters: [0] tasks, [1] cursor of the one-tile kernel, [2..3] executed pairs (lo, hi),
+                                 //           [4] cursor of the two-tile kernel
 
 // the counters start on a 16-byte boundary (the pair count is a 64-bit atomic), the tasks follow them
 __host__ __device__ inline size_t plan_counter_offset(int H) { return ((size_t)H * (kC + 1) + 3) & ~(size_t)3; }
@@ -98,7 +100,7 @@ __device__ __forceinline__ int block_excl_scan_256(int v, int* ws, int& total) {
   return inc - v + ws[warp];
 }
 
-// One CTA per head: key-cluster offsets, tasks of at most QT rows (a query
+// One CTA per head: key-cluster offsets, tasks of at most TASK_ROWS rows (a query
 // cluster is split evenly), longest-processing-time order inside the head.
 __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz, int H,
                                                    int N, int CQ, int* __restrict__ plan) {
@@ -121,7 +123,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, 
   int gbase = 0, ntask = 0;
   for (int hh = 0; hh <= h; ++hh) {
     int cnt = 0;
-    for (int c = tid; c < CQ; c += 256) cnt += cdiv(qsz[(size_t)hh * CQ + c], QT);
+    for (int c = tid; c < CQ; c += 256) cnt += cdiv(qsz[(size_t)hh * CQ + c], TASK_ROWS);
     int tot;
     block_excl_scan_256(cnt, ws, tot);
     if (hh < h) gbase += tot; else ntask = tot;
@@ -133,7 +135,7 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, 
   for (int base = 0; base < CQ; base += 256) {
     const int c = base + tid;
     const int v = c < CQ ? qsz[(size_t)h * CQ + c] : 0;
-    const int nt = cdiv(v, QT);
+    const int nt = cdiv(v, TASK_ROWS);
     int totq, tott;
     const int exq = block_excl_scan_256(v, ws, totq);
     const int ext = block_excl_scan_256(nt, ws, tott);
@@ -276,7 +278,11 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
 
   while (true) {
     __syncthreads();
-    if (tid == 0) sMisc[0] = atomicAdd(&pv.counters[1], 1);
+    if (tid == 0) {      // next task of at most QT rows (the two-tile kernel takes the others)
+      int i;
+      do { i = atomicAdd(&pv.counters[1], 1); } while (i < numTasks && pv.tasks[i].w > QT);
+      sMisc[0] = i;
+    }
     __syncthreads();
     const int ti = sMisc[0];
     if (ti >= numTasks || *abort_flag) break;
@@ -522,6 +528,392 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// ---------------------------------------------------------------------------
+// exact attention, tasks of QT + 1 .. TASK_ROWS rows
+// ---------------------------------------------------------------------------
+// Two row tiles share one K/V stream, so the union crosses L2 -> SM once per task
+// instead of once per 128 rows, and the roles are separated so that nobody who
+// computes ever waits on an issue queue:
+//   warps 0..3 / 4..7  softmax of row group 0 / 1: one thread per query row; S / P
+//                      and O of a group live in its own half of tensor memory
+//   warp 8             one lane issues every MMA (an MMA blocks its issuer while the
+//                      tensor pipe's queue is full)
+//   warps 10..15       stream K and V tiles into two-slot rings with four-row TMA gathers.
+//                      A gather blocks its warp for about 70 cycles per lane, one lane at a
+//                      time, but gathers of different warps overlap: six warps issue the
+//                      128 gathers of a tile pair, 21 or 22 each
+//   (warp 9 only takes part in the CTA-wide barriers: 16 warps keep four per scheduler)
+// Hand-offs are mbarriers: S[g] / O[g] (MMA done -> softmax), P[g] (softmax -> MMA),
+// fullK / fullV[s] (copy landed -> MMA), freeK / freeV[s] (both groups' MMA done -> copy),
+// fullQ[g].  Ring slot s holds tile g with g & 1 == s, where g counts the tiles this
+// CTA has processed; the n-th fill of a slot waits for phase n of its free barrier
+// (phase 0 is completed at start-up) and completes phase n of its full barrier.
+// Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so
+// that few registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16
+// over the columns S occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always
+// columns that were read before).  MASK: columns >= valid lie past the union and count as -inf.
+template <bool MASK>
+__device__ __forceinline__ void softmax_tile_2pass(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid,
+                                                   bool first, float sc) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tS_lane + c * 32, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(v[j]);
+      if (MASK && c * 32 + j >= valid) x = -INFINITY;
+      mx4[j & 3] = fmaxf(mx4[j & 3], x);
+    }
+  }
+  const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+  if (first) {
+    rs.m = mx;
+  } else {
+    const bool grow = mx > rs.m + kLazy;
+    if (__any_sync(0xffffffffu, grow)) {
+      const float mnew = grow ? mx : rs.m;
+      const float alpha = ex2_approx(rs.m - mnew);
+      rescale_rows(tO_lane, alpha);
+      rs.l *= alpha;
+      rs.m = mnew;
+    }
+  }
+  const float nm = -rs.m;
+  float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tS_lane + c * 32, v);
+    tmem_wait_ld();
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+      if (MASK) {
+        if (c * 32 + 2 * j >= valid) x0 = -INFINITY;
+        if (c * 32 + 2 * j + 1 >= valid) x1 = -INFINITY;
+      }
+      const float p0 = ex2_approx(fmaf(x0, sc, nm));
+      const float p1 = ex2_approx(fmaf(x1, sc, nm));
+      ls4[j & 3] += p0 + p1;
+      pk[j] = pack_bf2(p0, p1);
+    }
+    tmem_st16(tS_lane + c * 16, pk);
+  }
+  rs.l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+}
+
+constexpr int A2_COPY_WARPS = 6;
+constexpr int A2_THREADS = (10 + A2_COPY_WARPS) * 32;   // 8 softmax warps, the MMA warp, an idle warp, the copy warps
+constexpr int A2_SLOT = 2 * AT_TILE;                      // K tile, V tile
+constexpr int A2_OFF_SLOT = 2 * AT_TILE;                  // after the two Q tiles
+constexpr int A2_OFF_MISC = A2_OFF_SLOT + 2 * A2_SLOT;
+constexpr int A2_MAX_TILES = 1024;                        // tiles with a precomputed first run
+constexpr int A2_SMEM_INTS = A2_MAX_TILES + 8 + 2 * MAX_RUNS + 8 + 32;
+constexpr int A2_SMEM = A2_OFF_MISC + 256 + A2_SMEM_INTS * 4 + 1024;
+enum { B_S = 0, B_O = 2, B_P = 4, B_FULLK = 6, B_FULLV = 8, B_FREEK = 10, B_FREEV = 12, B_FULLQ = 14, B_COUNT = 16 };
+
+__global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
+    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
+    const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
+    __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
+    int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + A2_OFF_MISC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + A2_OFF_MISC + B_COUNT * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + A2_OFF_MISC + B_COUNT * 8 + 8);
+  int* sInt = reinterpret_cast<int*>(sm + A2_OFF_MISC + 256);
+  int* sTileRun = sInt;                           // [A2_MAX_TILES + 1] run that holds the first key of a tile
+  int* sRunStart = sInt + A2_MAX_TILES + 8;       // [MAX_RUNS]
+  int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
+  int* sMisc = sRunCum + MAX_RUNS + 8;            // [0] task, [1] runs; scan scratch from [8]
+
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = (warp >> 2) & 1, gt = tid & 127, gw = warp & 3;   // softmax warps: group, thread, warp in group
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < B_COUNT; ++i)
+      mbar_init(bars + i, (i >= B_P && i < B_P + 2) ? 4 : (i >= B_FREEK && i < B_FREEV + 2) ? 2 : 1);
+    mbar_init_fence();
+    // all ring slots start empty: complete phase 0 of the free barriers
+    for (int i = B_FREEK; i < B_FREEV + 2; ++i) { mbar_arrive(bars + i); mbar_arrive(bars + i); }
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  uint32_t tiles_done = 0, qcnt = 0;      // tiles / non-empty tasks this CTA has processed; every role counts alike
+  uint32_t phS = 0, phO = 0;              // softmax warps: phases of their group's S and O barriers
+  uint32_t phP[2] = {0, 0};               // MMA lane: phases of the P barriers
+  const int numTasks = pv.counters[0];
+  const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
+  constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) {      // next task of more than QT rows
+      int i;
+      do { i = atomicAdd(&pv.counters[4], 1); } while (i < numTasks && pv.tasks[i].w <= QT);
+      sMisc[0] = i;
+    }
+    __syncthreads();
+    const int ti = sMisc[0];
+    if (ti >= numTasks || *abort_flag) break;
+    const int4 tk = pv.tasks[ti];
+    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
+    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
+    const size_t rowbase = (size_t)h * N + qs;
+
+    if (kvlen == 0) {   // empty union: O = 0, lse = -inf
+      for (int i = tid; i < qrows * 16; i += A2_THREADS)
+        reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
+      for (int r = tid; r < qrows; r += A2_THREADS) attn_lse[rowbase + r] = -INFINITY;
+      continue;
+    }
+
+    // ---- runs of selected, non-empty key clusters (threads 0..127 hold 16 clusters each) ------
+    {
+      const int* koh = pv.k_off + (size_t)h * (kC + 1);
+      const uint32_t* ubr = ub + ((size_t)h * CQ + qc) * (kC / 32);
+      const bool scan = tid < 128;
+      const int c0 = scan ? tid * 16 : 0;
+      const uint32_t bw = scan ? (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu : 0u;
+      const int base0 = koh[c0];
+      bool pne0 = false;
+      if (scan && c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
+      int offs[17];
+      offs[0] = base0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
+      int cnt = 0, sz = 0;
+      {
+        bool pne = pne0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+          if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
+          pne = cne;
+        }
+      }
+      int* ws = sMisc + 8;
+      const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
+      if (scan && lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
+      __syncthreads();
+      int kbase = ic - cnt, pbase = is - sz;
+      for (int w = 0; w < warp && w < 4; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
+      const int totc = ws[0] + ws[1] + ws[2] + ws[3];
+      if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
+        if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
+      } else if (scan) {
+        bool pne = pne0;
+        int k = kbase, p = pbase;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+          if (cne) {
+            if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
+            p += offs[j + 1] - offs[j];
+          }
+          pne = cne;
+        }
+        if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
+      }
+      __syncthreads();
+      if (*abort_flag) break;
+    }
+    const int nruns = sMisc[1];
+    const int ntiles = cdiv(kvlen, KT);
+    const int rows0 = (qrows + 1) >> 1;                       // rows of group 0; group 1 takes the rest
+    const uint32_t g0 = tiles_done;
+    auto run_of = [&](int p, int lo, int hi) -> int {         // last run in [lo, hi] that starts at or before p
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (sRunCum[mid] <= p) lo = mid; else hi = mid - 1;
+      }
+      return lo;
+    };
+    // run of the first key of every tile: narrows the per-row searches of the copy warp
+    for (int i = tid; i <= ntiles && i <= A2_MAX_TILES; i += A2_THREADS)
+      sTileRun[i] = i < ntiles ? run_of(i * KT, 0, nruns - 1) : nruns - 1;
+    __syncthreads();
+
+    if (warp >= 10) {
+      // ================= copy warps: Q tiles of both groups, then the K / V stream ===============
+      const int cw = warp - 10;
+      const int op = cw + A2_COPY_WARPS * lane;      // gather of a 128-row tile pair: tile op >> 6 (K, V or
+      const bool has_op = op < 128;                    // Q0, Q1), 64-column block (op >> 5) & 1, rows 4 (op & 31) ..
+      const int ogrp = op >> 6, oblk = (op >> 5) & 1, orow = (op & 31) * 4;
+      if (has_op) {
+        const int off = ogrp ? rows0 : 0, nr = ogrp ? qrows - rows0 : rows0;
+        int r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)      // slots past the group repeat its first row
+          r[j] = h * N + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)];
+        if ((op & 63) == 0) mbar_arrive_expect_tx(bars + B_FULLQ + ogrp, AT_TILE);
+        tma_gather4(base + ogrp * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
+                    bars + B_FULLQ + ogrp);
+      }
+      for (int t = 0; t < ntiles; ++t) {
+        const uint32_t g = g0 + t, slot = g & 1u, par = (g >> 1) & 1u;
+        int r[4] = {0, 0, 0, 0};
+        if (has_op) {
+          const int lo = t < A2_MAX_TILES ? sTileRun[t] : 0;
+          const int hi = t + 1 <= A2_MAX_TILES ? sTileRun[t + 1] : nruns - 1;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int p = t * KT + orow + j;
+            int row = 0;                     // slots past the union read a real row; their scores are masked
+            if (p < kvlen) {
+              const int ru = run_of(p, lo, hi);
+              row = sRunStart[ru] + p - sRunCum[ru];
+            }
+            r[j] = h * N + row;
+          }
+        }
+        // every copy warp waits for both slots (in order, so its phase view stays exact), then issues
+        if (!mbar_wait(bars + B_FREEK + slot, par, abort_flag)) break;
+        if (!mbar_wait(bars + B_FREEV + slot, par, abort_flag)) break;
+        if (has_op) {
+          uint64_t* full = bars + (ogrp ? B_FULLV : B_FULLK) + slot;
+          if ((op & 63) == 0) mbar_arrive_expect_tx(full, AT_TILE);
+          tma_gather4(base + A2_OFF_SLOT + slot * A2_SLOT + ogrp * AT_TILE + oblk * (KT * 128) + orow * 128,
+                      ogrp ? &mapV : &mapK, oblk * 64, r[0], r[1], r[2], r[3], full);
+        }
+      }
+    } else if (warp == 8) {
+      // ================= MMA warp: one lane issues everything, group 0 then group 1 ===============
+      if (lane == 0) {
+        bool ok = true;
+        auto issue_qk = [&](int g, uint32_t tg) {      // S_g = Q_g K^T for ring tile tg
+          const uint32_t slot = tg & 1u;
+          if (g == 0) {      // group 1 follows group 0 on the same tile: one wait serves both
+            if (!mbar_wait(bars + B_FULLK + slot, (tg >> 1) & 1u, abort_flag)) { ok = false; return; }
+            tc_fence_after();
+          }
+          const uint32_t sQ = base + g * AT_TILE, sK = base + A2_OFF_SLOT + slot * A2_SLOT;
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
+            const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
+            umma_ss(tmem + g * 256, ad, bd, idescQK, s > 0 ? 1u : 0u);
+          }
+          umma_commit(bars + B_S + g);
+          umma_commit(bars + B_FREEK + slot);
+        };
+        tc_fence_after();
+        for (int g = 0; g < 2 && ok; ++g) {
+          if (!mbar_wait(bars + B_FULLQ + g, qcnt & 1u, abort_flag)) { ok = false; break; }
+          issue_qk(g, g0);
+        }
+        for (int t = 0; t < ntiles && ok; ++t) {
+          const uint32_t tg = g0 + t, slot = tg & 1u;
+          const uint32_t sV = base + A2_OFF_SLOT + slot * A2_SLOT + AT_TILE;
+          for (int g = 0; g < 2 && ok; ++g) {
+            if (!mbar_wait(bars + B_P + g, phP[g], abort_flag)) { ok = false; break; }    // P_g is in tensor memory
+            phP[g] ^= 1u;
+            if (g == 0 && !mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t tS = tmem + g * 256, tO = tS + 128;
+#pragma unroll
+            for (int s8 = 0; s8 < 8; ++s8) {
+              const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
+              umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+            }
+            umma_commit(bars + B_O + g);
+            umma_commit(bars + B_FREEV + slot);
+            if (t + 1 < ntiles) issue_qk(g, tg + 1);
+          }
+        }
+      }
+    } else if (warp < 8) {
+      // ================= softmax warps: 128 threads per group, one query row each =================
+      const int myoff = grp ? rows0 : 0, myrows = grp ? qrows - rows0 : rows0;
+      const bool warp_has_rows = gw * 32 < myrows;
+      const uint32_t tS = tmem + grp * 256, tO = tS + 128;
+      const uint32_t tS_lane = tmem_addr(tS, gw * 32, 0), tO_lane = tmem_addr(tO, gw * 32, 0);
+      uint64_t* barS = bars + B_S + grp;
+      uint64_t* barO = bars + B_O + grp;
+      RowState rs;
+      rs.m = -INFINITY;
+      rs.l = 0.f;
+      bool dead = false;
+      for (int t = 0; t < ntiles; ++t) {
+        if (!mbar_wait(barS, phS, abort_flag)) { dead = true; break; }
+        phS ^= 1u;
+        if (t > 0) {      // P V of tile t - 1 finished before Q K^T of tile t: this only tracks the phase
+          if (!mbar_wait(barO, phO, abort_flag)) { dead = true; break; }
+          phO ^= 1u;
+        }
+        tc_fence_after();
+        // A warp whose rows all lie past the group's last row skips the arithmetic: its P rows stay
+        // whatever S held, which only reaches O rows that are never stored.
+        if (warp_has_rows) {
+          const int valid = kvlen - t * KT;
+          if (valid >= KT) softmax_tile_2pass<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
+          else softmax_tile_2pass<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + B_P + grp);
+      }
+      if (!dead) {
+        if (!mbar_wait(barO, phO, abort_flag)) dead = true;
+        else phO ^= 1u;
+      }
+      if (!dead) {
+        tc_fence_after();
+        if (warp_has_rows) {
+          const float inv = 1.0f / rs.l;
+          const bool wr = gt < myrows;
+          uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + myoff + gt) * kD);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO_lane + c * 32, v);
+            tmem_wait_ld();
+            if (wr) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 o;
+                o.x = pack_bf2(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+                o.y = pack_bf2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+                o.z = pack_bf2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+                o.w = pack_bf2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+                dst[c * 4 + g] = o;
+              }
+            }
+          }
+          if (wr) attn_lse[rowbase + myoff + gt] = (rs.m + log2f(rs.l)) * 0.6931471805599453f;
+        }
+        tc_fence_before();
+      }
+    }
+    tiles_done += ntiles;
+    ++qcnt;
+  }
+  if (*abort_flag) {
+    if (tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+    // a wait gave up: let tile copies still in flight land before the shared memory is released
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
 }
 
 // ---------------------------------------------------------------------------
@@ -797,11 +1189,14 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   split_ws(ws, H, N, &attn_out, &attn_lse);
   const PlanView pv = plan_view(plan, H, N, CQ);
   // the task cursor is the only per-dispatch state of a prepared plan
-  if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
+  if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess ||
+      cudaMemsetAsync(pv.counters + 4, 0, sizeof(int), st) != cudaSuccess)
+    return T2T_ERR_CUDA;
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess)
+  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+      cudaFuncSetAttribute(attn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
   // tensor maps over q, kp, vp as [H * N, 128] matrices: the kernel fetches tile rows four at a time
   CUtensorMap mq, mk, mv;
@@ -809,6 +1204,9 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   if (!make_row_gather_map(&mq, q, rows) || !make_row_gather_map(&mk, kp, rows) ||
       !make_row_gather_map(&mv, vp, rows))
     return T2T_ERR_CUDA;
+  // tasks above 128 rows first (one CTA per SM, two row tiles per K/V stream), then the others
+  attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out,
+                                                 attn_lse, plan, H, N, CQ, d_status);
   attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
                                              plan, H, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
