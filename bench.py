@@ -300,10 +300,10 @@ def run_ours(args, rank, world, local_rank):
     roofline = None
     if t_attn > 0:
         ach = flops / (t_attn * 1e-3) / 1e12
-        # DRAM bytes of one launch: 256.4 MB (dram__bytes_read + write) in the ncu capture of the 8-head 480p
-        # case (profiles/attn_kernel_480p_8heads.md), scaled by the rows processed (q, kp, vp read once and the
-        # exact output written once: traffic is proportional to H * N)
-        traffic = 256.4e6 * (Hl * float(N)) / (8 * 32760.0)
+        # DRAM bytes of the two attention kernels: 381.2 MB (dram__bytes_read + write) in the ncu capture of the
+        # 8-head 480p case (profiles/attn_kernels_480p_8heads.md), scaled by the rows processed (each kernel
+        # reads q, kp, vp once; the exact output is written once: traffic is proportional to H * N)
+        traffic = 381.2e6 * (Hl * float(N)) / (8 * 32760.0)
         roofline = {"kernel": "attn2_kernel + attn_kernel (exact tile attention)", "bound": "tensor", "achieved": ach, "peak": pk["tf"],
                     "unit": "TFLOP/s", "frac": ach / pk["tf"], "traffic": traffic,
                     "traffic_source": "ncu 480p x 8 heads capture scaled by rows", "peak_source": pk["src"] +
