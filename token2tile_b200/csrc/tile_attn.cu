@@ -546,7 +546,8 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
 //                      128 gathers of a tile pair, 21 or 22 each
 //   (warp 9 only takes part in the CTA-wide barriers: 16 warps keep four per scheduler)
 // Hand-offs are mbarriers: S[g] / O[g] (MMA done -> softmax), P[g] (softmax -> MMA),
-// fullK / fullV[s] (copy landed -> MMA), freeK / freeV[s] (both groups' MMA done -> copy),
+// fullK / fullV[s] (copy landed -> MMA), freeK / freeV[s] (both groups' MMA done -> copy: one
+// commit after group 1's MMA, which the tensor pipe runs after group 0's),
 // fullQ[g].  Ring slot s holds tile g with g & 1 == s, where g counts the tiles this
 // CTA has processed; the n-th fill of a slot waits for phase n of its free barrier
 // (phase 0 is completed at start-up) and completes phase n of its full barrier.
@@ -646,10 +647,10 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(bars + i, (i >= B_P && i < B_P + 2) ? 4 : (i >= B_FREEK && i < B_FREEV + 2) ? 2 : 1);
+      mbar_init(bars + i, (i >= B_P && i < B_P + 2) ? 4 : 1);
     mbar_init_fence();
     // all ring slots start empty: complete phase 0 of the free barriers
-    for (int i = B_FREEK; i < B_FREEV + 2; ++i) { mbar_arrive(bars + i); mbar_arrive(bars + i); }
+    for (int i = B_FREEK; i < B_FREEV + 2; ++i) mbar_arrive(bars + i);
   }
   tc_fence_before();
   __syncthreads();
@@ -796,14 +797,12 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       }
     } else if (warp == 8) {
       // ================= MMA warp: one lane issues everything, group 0 then group 1 ===============
+      // The lane is the busiest resource of the kernel (an MMA of this shape occupies the tensor pipe
+      // for ~90 cycles and the issue blocks for as long), so it waits for the tiles, which land early,
+      // before it waits for a group's P, and then issues P V and the next Q K^T back to back.
       if (lane == 0) {
         bool ok = true;
-        auto issue_qk = [&](int g, uint32_t tg) {      // S_g = Q_g K^T for ring tile tg
-          const uint32_t slot = tg & 1u;
-          if (g == 0) {      // group 1 follows group 0 on the same tile: one wait serves both
-            if (!mbar_wait(bars + B_FULLK + slot, (tg >> 1) & 1u, abort_flag)) { ok = false; return; }
-            tc_fence_after();
-          }
+        auto mma_qk = [&](int g, uint32_t slot) {      // S_g = Q_g K^T for the K tile in ring slot `slot`
           const uint32_t sQ = base + g * AT_TILE, sK = base + A2_OFF_SLOT + slot * A2_SLOT;
 #pragma unroll
           for (int s = 0; s < 8; ++s) {
@@ -812,20 +811,26 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
             umma_ss(tmem + g * 256, ad, bd, idescQK, s > 0 ? 1u : 0u);
           }
           umma_commit(bars + B_S + g);
-          umma_commit(bars + B_FREEK + slot);
+          if (g == 1) umma_commit(bars + B_FREEK + slot);      // covers group 0's MMAs too: same issuer, in order
         };
         tc_fence_after();
-        for (int g = 0; g < 2 && ok; ++g) {
-          if (!mbar_wait(bars + B_FULLQ + g, qcnt & 1u, abort_flag)) { ok = false; break; }
-          issue_qk(g, g0);
+        ok = mbar_wait(bars + B_FULLQ + 0, qcnt & 1u, abort_flag) && mbar_wait(bars + B_FULLQ + 1, qcnt & 1u, abort_flag) &&
+             mbar_wait(bars + B_FULLK + (g0 & 1u), (g0 >> 1) & 1u, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          mma_qk(0, g0 & 1u);
+          mma_qk(1, g0 & 1u);
         }
         for (int t = 0; t < ntiles && ok; ++t) {
           const uint32_t tg = g0 + t, slot = tg & 1u;
+          const bool more = t + 1 < ntiles;
           const uint32_t sV = base + A2_OFF_SLOT + slot * A2_SLOT + AT_TILE;
-          for (int g = 0; g < 2 && ok; ++g) {
+          if (!mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) break;
+          if (more && !mbar_wait(bars + B_FULLK + (slot ^ 1u), ((tg + 1) >> 1) & 1u, abort_flag)) break;
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
             if (!mbar_wait(bars + B_P + g, phP[g], abort_flag)) { ok = false; break; }    // P_g is in tensor memory
             phP[g] ^= 1u;
-            if (g == 0 && !mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t tS = tmem + g * 256, tO = tS + 128;
 #pragma unroll
@@ -834,8 +839,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
               umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
             }
             umma_commit(bars + B_O + g);
-            umma_commit(bars + B_FREEV + slot);
-            if (t + 1 < ntiles) issue_qk(g, tg + 1);
+            if (g == 1) umma_commit(bars + B_FREEV + slot);
+            if (more) mma_qk(g, slot ^ 1u);
           }
         }
       }
