@@ -253,7 +253,7 @@ def _select(lib, QU, cks, kcounts, qperm, qcounts, ns, pin_tail=0):
     # the tensor-core path and the all-exact path must agree bit for bit
     assert torch.equal(rowcnt, rowcnt_x)
     assert torch.equal(unip, unip_x)
-    q = ws.view(torch.int32).view(H, 2 * N + 1)[:, 0]
+    q = ws.view(torch.int32)[: H * (2 * N + 1)].view(H, 2 * N + 1)[:, 0]      # per head: count, then the queue
     _select.requeued = int(q.sum().item())
     return unip.cpu(), rowcnt.cpu()
 

@@ -8,10 +8,10 @@
 // segment's bitmap, flushed to the cluster's bitmap at the end).  A tcgen05 MMA
 // (128 x 128 x 32 per chunk of centroids, all 2048 centroids resident in shared
 // memory) gives approximate scores s~ in TMEM, and each row is settled in three
-// streaming passes over them:
+// steps, two of them streaming passes over the scores:
 //
-//   P1  row maximum (the row mean is q . mean centroid, the minimum is bounded by
-//       -||q|| max ||c||, neither needs a pass);
+//   P1  row mean and deviation from the head's centroid moments (q . mean centroid,
+//       q^T (mean c c^T) q): no pass; the scores lie in [-||q|| max ||c||, ||q|| max ||c||];
 //   P2  size-weighted histogram of s~ over [mean, max] (refined if the threshold
 //       bucket is crowded) -> the bucket [x_lo, x_hi] in which the running token
 //       count first reaches ns;
@@ -38,6 +38,7 @@ constexpr int ST_B = 64;                   // histogram buckets
 constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
 constexpr int ST_MAX_ITERS = 5;
+constexpr int kMomFloats = 32 + 32 * 32;   // per head: mean centroid, second-moment matrix
 constexpr int ST_STRAGGLERS = 8;           // this few unsettled rows of a tile go to the exact kernel instead of another pass
 
 constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
@@ -74,7 +75,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
     const int* __restrict__ kcounts, const int* __restrict__ qperm, const int* __restrict__ tile_sizes,
     const int* __restrict__ ns_ptr, int* __restrict__ unip, int* __restrict__ rowcnt, int N, int CQ,
-    int* __restrict__ fixq, int* __restrict__ status) {
+    int* __restrict__ fixq, const float* __restrict__ mom, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
@@ -271,6 +272,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         }
       }
       const float bound = sqrtf(qn) * cmaxnorm;
+      sRowF[R_MAX * 128 + r] = bound;            // no score exceeds ||q|| max ||c||
       sRowF[R_EPS * 128 + r] = 6.103515625e-05f * bound + 1.0e-30f;
       sRowF[R_MIN * 128 + r] = -bound - 1.0f;
       sRowI[R_STATE * 128 + r] =
@@ -280,38 +282,58 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       sRowI[R_SIZEA * 128 + r] = 0;
     }
 
-    // ---- P1: row maximum, mean and standard deviation of the approximate scores ----------
+    // ---- P1: mean and standard deviation of the row's scores, without a pass over them ------------
+    // sum_c q.c = q . sum_c c and sum_c (q.c)^2 = q^T (sum_c c c^T) q: the head's centroid moments (a
+    // 32-vector and a 32 x 32 matrix, fp32) give both in 1056 multiply-adds per row.  Each column group
+    // takes eight rows of the matrix.  The statistics only place the first histogram range.
     {
-      float mx0 = -INFINITY, mx1 = -INFINITY, s1a = 0.f, s1b = 0.f, s2a = 0.f, s2b = 0.f;
-      stream([&](int, const uint32_t(&v)[32]) {
+      const float* mh = mom + (size_t)blockIdx.y * kMomFloats;
+      float qv[32];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float a = __uint_as_float(v[j]), b2 = __uint_as_float(v[j + 1]);
-          mx0 = fmaxf(mx0, a); mx1 = fmaxf(mx1, b2);
-          s1a += a; s1b += b2;
-          s2a = fmaf(a, a, s2a); s2b = fmaf(b2, b2, s2b);
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, q4));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { qv[q4 * 8 + 2 * e] = bf_lo(ws[e]); qv[q4 * 8 + 2 * e + 1] = bf_hi(ws[e]); }
+      }
+      float qa[8];      // elements 8 g .. 8 g + 7 of the row: chunk g
+      {
+        const uint4 w = *reinterpret_cast<const uint4*>(sm + OFF_A + sw128(r, g));
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { qa[2 * e] = bf_lo(ws[e]); qa[2 * e + 1] = bf_hi(ws[e]); }
+      }
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float* grow = mh + 32 + (8 * g + i) * 32;
+        float t0 = 0.f, t1 = 0.f;
+#pragma unroll
+        for (int b2 = 0; b2 < 32; b2 += 2) {
+          t0 = fmaf(__ldg(grow + b2), qv[b2], t0);
+          t1 = fmaf(__ldg(grow + b2 + 1), qv[b2 + 1], t1);
         }
-      });
-      sPart[(0 * 4 + g) * 128 + r] = fmaxf(mx0, mx1);
-      sPart[(1 * 4 + g) * 128 + r] = s1a + s1b;
-      sPart[(2 * 4 + g) * 128 + r] = s2a + s2b;
+        s2 = fmaf(qa[i], t0 + t1, s2);
+        s1 = fmaf(qa[i], __ldg(mh + 8 * g + i), s1);
+      }
+      sPart[(1 * 4 + g) * 128 + r] = s1;
+      sPart[(2 * 4 + g) * 128 + r] = s2;
     }
     __syncthreads();
     if (g == 0 && sRowI[R_STATE * 128 + r] == RS_SEARCH) {
-      float M = -INFINITY, s1 = 0.f, s2 = 0.f;
+      float mean = 0.f, s2 = 0.f;
 #pragma unroll
       for (int gg = 0; gg < 4; ++gg) {
-        M = fmaxf(M, sPart[(0 * 4 + gg) * 128 + r]);
-        s1 += sPart[(1 * 4 + gg) * 128 + r];
+        mean += sPart[(1 * 4 + gg) * 128 + r];
         s2 += sPart[(2 * 4 + gg) * 128 + r];
       }
-      const float mean = s1 * (1.0f / kC);
-      const float sd = sqrtf(fmaxf(s2 * (1.0f / kC) - mean * mean, 1.0e-20f));
-      const bool finite = fabsf(M) < INFINITY && fabsf(s2) < INFINITY;
+      const float M = sRowF[R_MAX * 128 + r];
+      const float sd = sqrtf(fmaxf(s2 - mean * mean, 1.0e-20f));
+      const bool finite = fabsf(M) < INFINITY && fabsf(s2) < INFINITY && fabsf(mean) < INFINITY;
       // First range: 2.5 standard deviations around the score a fraction ns / N of a bell-shaped
       // distribution would exceed (inverse normal tail, Abramowitz-Stegun 26.2.23).  Everything above the
       // range is counted in an overflow bucket.  The range only has to be a good guess: the search continues
-      // above or below it when the running token count says so.
+      // above it (up to the bound ||q|| max ||c||) or below it when the running token count says so.
       const float f = fminf(0.5f, fmaxf((float)ns / (float)N, 1.0e-6f));
       const float tt = sqrtf(-2.0f * __logf(f));
       const float z = tt - (2.515517f + tt * (0.802853f + tt * 0.010328f)) /
@@ -320,7 +342,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       const int ovf = hi < M ? 1 : 0;
       hi = ovf ? hi : M;
       const float lo = fminf(mean + (z - 1.25f) * sd, hi);
-      sRowF[R_MAX * 128 + r] = M;
       sRowF[R_HI * 128 + r] = hi;
       sRowF[R_LO * 128 + r] = lo;
       sRowI[R_OVF * 128 + r] = ovf;
@@ -591,7 +612,26 @@ __global__ void pin_bit_kernel(int* __restrict__ unip, int rows) {
   if (i < rows) atomicOr(reinterpret_cast<unsigned*>(unip) + (size_t)i * 64 + 63, 0x80000000u);
 }
 
-size_t select_ws_bytes(int H, int N) { return (size_t)H * (2 * (size_t)N + 1) * sizeof(int); }
+// First two moments of a head's scaled key centroids: mom[h] = { mean_c c (32), mean_c c c^T (32 x 32) }.
+__global__ void __launch_bounds__(1024) centroid_moments_kernel(const __nv_bfloat16* __restrict__ cks,
+                                                                float* __restrict__ mom) {
+  const int h = blockIdx.x, a = threadIdx.x >> 5, b = threadIdx.x & 31;
+  const __nv_bfloat16* ch = cks + (size_t)h * kC * kR;
+  float g0 = 0.f, g1 = 0.f, m0 = 0.f;
+  for (int c = 0; c < kC; c += 2) {
+    const float xa0 = bf_to_f(ch[c * kR + a]), xb0 = bf_to_f(ch[c * kR + b]);
+    const float xa1 = bf_to_f(ch[(c + 1) * kR + a]), xb1 = bf_to_f(ch[(c + 1) * kR + b]);
+    g0 = fmaf(xa0, xb0, g0);
+    g1 = fmaf(xa1, xb1, g1);
+    m0 += xb0 + xb1;
+  }
+  float* mh = mom + (size_t)h * kMomFloats;
+  mh[32 + a * 32 + b] = (g0 + g1) * (1.0f / kC);
+  if (a == 0) mh[b] = m0 * (1.0f / kC);
+}
+
+static size_t select_queue_bytes(int H, int N) { return ((size_t)H * (2 * (size_t)N + 1) * sizeof(int) + 255) & ~(size_t)255; }
+size_t select_ws_bytes(int H, int N) { return select_queue_bytes(H, N) + (size_t)H * kMomFloats * sizeof(float); }
 
 }  // namespace t2t
 
@@ -610,14 +650,16 @@ extern "C" int t2t_score_select_union(const void* QU, const void* cks, const voi
     return t2t_score_select_union_exact(QU, cks, kcounts, qperm, tile_sizes, ns, unip, rowcnt, H, N, CQ, pin_tail,
                                         st);
   int* fixq = (int*)ws;
-  if (cudaMemsetAsync(fixq, 0, select_ws_bytes(H, N), st) != cudaSuccess ||
+  float* mom = reinterpret_cast<float*>((char*)ws + select_queue_bytes(H, N));
+  centroid_moments_kernel<<<H, 1024, 0, st>>>((const __nv_bfloat16*)cks, mom);
+  if (cudaMemsetAsync(fixq, 0, select_queue_bytes(H, N), st) != cudaSuccess ||
       cudaMemsetAsync(unip, 0, (size_t)H * CQ * 64 * sizeof(int), st) != cudaSuccess)
     return T2T_ERR_CUDA;
   if (cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
   select_tc_kernel<<<dim3(cdiv(N, 128), H), ST_THREADS, ST_SMEM, st>>>(
       (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const int*)qperm,
-      (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, fixq, d_status);
+      (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, fixq, mom, d_status);
   if (pin_tail > 0) pin_bit_kernel<<<cdiv(H * CQ, 256), 256, 0, st>>>((int*)unip, H * CQ);
   if (cudaGetLastError() != cudaSuccess) return T2T_ERR_CUDA;
   return launch_select_fix((const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, ns, (int*)unip,
