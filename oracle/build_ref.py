@@ -3,7 +3,7 @@ select_union CUDA sources, compiled where they lie in the reference checkout
 with the reference's flags (deploy_step.py:46-47, 95-97) except for the target
 architecture (sm_100a instead of sm_90a), plus the thin C wrapper ref_wrap.cu.
 
-    python oracle/build_ref.py [/root/reference]
+    python oracle/build_ref.py [REFERENCE_CHECKOUT]
 
 The output is a checker used by tests/test_gpu_ref_pin.py to pin the CPU oracle
 against the reference's real kernels.  The reference's tile_attn sources are

@@ -3,7 +3,7 @@
 
 Run in a container that has the reference checkout:
 
-    python tests/golden/make_online_u_golden.py [/root/reference]
+    python tests/golden/make_online_u_golden.py [REFERENCE_CHECKOUT]
 
 The fixture stores the seeds, not the inputs: the test regenerates q and k with
 the same generator calls.
