@@ -201,6 +201,13 @@ int t2t_umma_selftest(const void* A, const void* B, const void* V, float* S_out,
 int t2t_gather4_selftest(const void* src, int rows, const int* gidx, void* out, int* d_status,
                          cudaStream_t stream);
 
+/* Bounded-wait self-test: one CTA waits on a barrier that nothing arrives on, with a
+ * spin limit of about a millisecond, and leaves the way the production kernels do when
+ * a wait gives up: *d_status becomes 1 (wait timed out), d_out[0..1] = 0 (both warps'
+ * waits returned "gave up": the first by its limit, the second by the abort flag).  The
+ * kernel always terminates.  No counterpart in the reference. */
+int t2t_wait_timeout_selftest(int* d_status, int* d_out, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

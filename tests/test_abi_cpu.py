@@ -43,6 +43,7 @@ def test_null_and_bad_arguments_are_rejected(lib):
     assert lib.t2t_tile_attn_plan(0, 0, 0, 0, 2, 4096, 32, 0) == 1
     assert lib.t2t_umma_selftest(0, 0, 0, 0, 0, 0, 0) == 1
     assert lib.t2t_gather4_selftest(0, 0, 0, 0, 0, 0) == 1
+    assert lib.t2t_wait_timeout_selftest(0, 0, 0) == 1
 
 
 def test_operator_dir_points_at_the_sources():

@@ -48,6 +48,18 @@ def test_gather4_selftest(lib):
     assert torch.equal(unsw, want)
 
 
+def test_bounded_wait_gives_up_cleanly(lib):
+    """A wait that can never complete ends by its spin limit, raises the abort
+    flag for the other warps, reports through the status word, and the context
+    stays usable."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((2,), -1, dtype=torch.int32, device=DEV)
+    _ok(lib.t2t_wait_timeout_selftest(status.data_ptr(), out.data_ptr(), _st()))
+    torch.cuda.synchronize()
+    assert int(status.item()) == 1 and out.tolist() == [0, 0]
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0      # the device still works
+
+
 def test_umma_selftest(lib):
     g = torch.Generator().manual_seed(7)
     A = (torch.randn(128, 128, generator=g) * 0.5).to(BF)

@@ -44,6 +44,7 @@ SIGNATURES = {
     "t2t_tile_attn_plan_info": (_I, [_P, _I, _I, _I, _P, _P]),
     "t2t_umma_selftest": (_I, [_P, _P, _P, _P, _P, _P, _P]),
     "t2t_gather4_selftest": (_I, [_P, _I, _P, _P, _P, _P]),
+    "t2t_wait_timeout_selftest": (_I, [_P, _P, _P]),
 }
 
 

@@ -88,8 +88,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // raised `*abort_flag`); the caller must then leave its loops, skip further
 // waits and fall through to the kernel's common exit so TMEM is released.
 constexpr uint32_t kWaitSpinLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kWaitSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait_limited(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                  uint32_t limit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (it > 64) {
       if (*abort_flag) return false;
@@ -98,6 +99,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   *abort_flag = 1;
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, kWaitSpinLimit);
 }
 
 // ---- TMA row gather ----------------------------------------------------------

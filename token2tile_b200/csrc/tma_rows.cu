@@ -71,9 +71,41 @@ __global__ void __launch_bounds__(128) gather4_selftest_kernel(const __grid_cons
   }
 }
 
+// The give-up path of the bounded waits, exercised on purpose: a barrier that nobody arrives on, a
+// short spin limit, and the same exit sequence as the production kernels (raise the abort flag, report
+// through the status word, return).  The kernel always terminates.
+__global__ void __launch_bounds__(64) wait_timeout_selftest_kernel(int* __restrict__ status, int* __restrict__ out) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  volatile int* abort_flag = &abort_word;
+  const int tid = threadIdx.x;
+  if (tid == 0) {
+    abort_word = 0;
+    mbar_init(&bar, 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+  // warp 0 runs into the limit; warp 1 starts later and leaves as soon as it sees the abort flag
+  bool ok;
+  if (tid < 32) {
+    ok = mbar_wait_limited(&bar, 0, abort_flag, 1u << 10);
+  } else {
+    ok = mbar_wait_limited(&bar, 0, abort_flag, kWaitSpinLimit);
+  }
+  if (tid == 0 || tid == 32) out[tid >> 5] = ok ? 1 : 0;
+  __syncthreads();
+  if (tid == 0 && *abort_flag) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+}
+
 }  // namespace t2t
 
 using namespace t2t;
+
+extern "C" int t2t_wait_timeout_selftest(int* d_status, int* d_out, cudaStream_t st) {
+  if (!d_status || !d_out) return T2T_ERR_ARG;
+  wait_timeout_selftest_kernel<<<1, 64, 0, st>>>(d_status, d_out);
+  return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
+}
 
 extern "C" int t2t_gather4_selftest(const void* src, int rows, const int* gidx, void* out, int* d_status,
                                     cudaStream_t st) {
