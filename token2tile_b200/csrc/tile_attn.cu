@@ -1057,13 +1057,16 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
     const uint32_t mw[4] = {mw4.x, mw4.y, mw4.z, mw4.w};
     float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-    for (int i = 0; i < TL_C; ++i) {
-      // the score is rounded to fp16 exactly as the selection saw it
-      const float g = __half2float(__float2half_rn(s[i])) * LOG2E;
-      s[i] = ((mw[i >> 5] >> (i & 31)) & 1u) ? -INFINITY : g;
-      mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
+    for (int i = 0; i < TL_C; i += 2) {
+      // the scores are rounded to fp16 exactly as the selection saw them (one packed conversion per pair);
+      // they stay in natural-log units here, log2(e) is folded into the exponent's multiply-add below
+      const __half2 h2 = __floats2half2_rn(s[i], s[i + 1]);
+      const float2 g = __half22float2(h2);
+      s[i] = ((mw[i >> 5] >> (i & 31)) & 1u) ? -INFINITY : g.x;
+      s[i + 1] = ((mw[(i + 1) >> 5] >> ((i + 1) & 31)) & 1u) ? -INFINITY : g.y;
+      mx4[(i >> 1) & 3] = fmaxf(mx4[(i >> 1) & 3], fmaxf(s[i], s[i + 1]));
     }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * LOG2E;
     const bool grow = mx > m + kLazy || (m == -INFINITY && mx > -INFINITY);
     if (__any_sync(0xffffffffu, grow)) {
       const float mnew = grow ? mx : m;
@@ -1077,8 +1080,8 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
     uint32_t pk[TL_C / 2];
 #pragma unroll
     for (int i = 0; i < TL_C / 2; ++i) {
-      const float p0 = ex2_approx(s[2 * i] + nm);
-      const float p1 = ex2_approx(s[2 * i + 1] + nm);
+      const float p0 = ex2_approx(fmaf(s[2 * i], LOG2E, nm));
+      const float p1 = ex2_approx(fmaf(s[2 * i + 1], LOG2E, nm));
       ps4[i & 3] = fmaf(p1, sCnt[2 * i + 1], fmaf(p0, sCnt[2 * i], ps4[i & 3]));
       pk[i] = pack_bf2(p0, p1);
     }
