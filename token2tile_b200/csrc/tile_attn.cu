@@ -100,8 +100,8 @@ __device__ __forceinline__ int block_excl_scan_256(int v, int* ws, int& total) {
   return inc - v + ws[warp];
 }
 
-// One CTA per head: key-cluster offsets, tasks of at most TASK_ROWS rows (a query
-// cluster is split evenly), longest-processing-time order inside the head.
+// One CTA per head: key-cluster offsets, tasks of at most TASK_ROWS rows (a larger query cluster
+// gives full tasks and one remainder task), longest-processing-time order inside the head.
 __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz, int H,
                                                    int N, int CQ, int* __restrict__ plan) {
   __shared__ int ws[16];
@@ -141,7 +141,8 @@ __global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, 
     const int ext = block_excl_scan_256(nt, ws, tott);
     int s = qrun + exq;
     for (int i = 0; i < nt; ++i) {
-      const int rows = v / nt + (i < v % nt ? 1 : 0);
+      // full tasks first, the remainder last: a remainder of at most QT rows costs one row tile instead of two
+      const int rows = i + 1 < nt ? TASK_ROWS : v - (nt - 1) * TASK_ROWS;
       pv.tasks[gbase + trun + ext + i] = make_int4(h, c, s, rows);
       s += rows;
     }
