@@ -34,7 +34,7 @@ sys.path.insert(0, str(ROOT))
 
 WORKLOAD = dict(name="wan2.1-14b-720p-self-attention-layer", H=40, grid="720p", N=75600, CQ=512, D=128,
                 s_frac=0.015)
-KERNELS_REBUILD = 2 + 21 + 2 + 1 + 2 + 3  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), select+fix, gather, plan, attention (two kernels) + merge
+KERNELS_REBUILD = 2 + 21 + 3 + 1 + 2 + 3  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), centroid moments+select+fix, gather, plan, attention (two kernels) + merge
 KERNELS_REUSE = 1 + 1 + 3 + 3   # project q, gather k, value stats, attention (two kernels) + merge
 METRIC = "t2t_attn_ms_per_layer"
 UNIT = "ms/layer"
