@@ -179,3 +179,29 @@ def test_two_devices_give_the_same_bits(small_case):
             torch.cuda.synchronize(dev)
             outs.append(o.cpu())
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
+
+
+@pytest.mark.parametrize("CQ", [4, 7])
+def test_operator_with_few_large_query_clusters(small_case, CQ):
+    """Query clusters of ~600-1000 rows: several full 256-row attention tasks plus
+    a remainder per cluster (both attention kernels), an odd cluster count."""
+    from token2tile_b200 import MaskedStepDeploy
+    c = dict(small_case, CQ=CQ)
+    H, N = c["H"], c["N"]
+    op = MaskedStepDeploy(H, N, CQ, s_frac=0.03)
+    q, k, v = (c[n].to(DEV) for n in "qkv")
+    state = op.init_state(q, k, warm_iters=2, seed=1)
+    before = {n: t.cpu().clone() for n, t in state.items()}
+    out = op.step(q, k, v, state).cpu().float()
+    torch.cuda.synchronize()
+    assert op.device_status() == 0
+    km, cks, unip = _check_structure(op, c, before, op.ns)
+    sizes = km["qcounts"]
+    assert int(sizes.max()) > 256                    # at least one cluster is split into several tasks
+    tasks, pairs = op.plan_info()
+    want_tasks = int(((sizes + 255) // 256).sum())
+    assert tasks == want_tasks
+    o, lse = O.exact_attention(c["q"], c["k"], c["v"], km["qlab"], km["klab"], unip, op.scale)
+    want = O.residual_merge(o, lse, op.QU.cpu(), cks, km["sumv"], km["lam"], km["kcounts"], unip, km["qlab"], 1.0)
+    err = (out - want).abs()
+    assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
