@@ -205,3 +205,25 @@ def test_operator_with_few_large_query_clusters(small_case, CQ):
     want = O.residual_merge(o, lse, op.QU.cpu(), cks, km["sumv"], km["lam"], km["kcounts"], unip, km["qlab"], 1.0)
     err = (out - want).abs()
     assert err.max() < 2e-2 and err.mean() < 2e-3, (err.max(), err.mean())
+
+
+def test_module_level_helpers_of_the_reference_module(small_case):
+    """fast_assign / fused_update_vstats / fast_gather, the names the reference's
+    hosts reach through the operator module, against the oracle."""
+    import token2tile_b200.deploy_step as D
+    c = small_case
+    QU = O.project(c["q"], c["state"]["Uq"], BF)
+    cq = c["state"]["cq"]
+    lab = D.fast_assign(QU.to(DEV), cq.to(DEV))
+    assert torch.equal(lab.cpu(), O.assign(QU, cq, 0))
+    newc, counts, mean_v = D.fused_update_vstats(QU.to(DEV), lab, cq.to(DEV), None)
+    want_c, want_counts = O.fixed_point_mean(QU, lab.cpu(), cq, BF)
+    assert mean_v is None and torch.equal(counts.cpu(), want_counts)
+    assert torch.equal(newc.cpu().view(torch.int16), want_c.view(torch.int16))
+    g = torch.Generator().manual_seed(4)
+    p = torch.stack([torch.randperm(c["N"], generator=g) for _ in range(c["H"])])
+    got = D.fast_gather(c["k"].to(DEV), p.to(DEV))
+    assert torch.equal(got.cpu().view(torch.int16),
+                       torch.gather(c["k"], 1, p[..., None].expand(-1, -1, 128)).view(torch.int16))
+    with pytest.raises(NotImplementedError):
+        D.fused_update_vstats(QU.to(DEV), lab, cq.to(DEV), c["v"].to(DEV))

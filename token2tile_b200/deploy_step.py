@@ -94,6 +94,81 @@ def _stream_ptr(stream) -> int:
     return stream.cuda_stream
 
 
+# ---------------------------------------------------------------------------
+# module-level helpers of the reference operator module
+# ---------------------------------------------------------------------------
+# The reference's deploy_step imports fast_assign, fast_gather and
+# fused_update_vstats into its namespace (deploy_step.py:40-42) and its hosts call
+# them through the module (integrations/sglang/backend/t2t_attn.py:275-278).  The
+# same names here run the library's kernels on the current stream.
+
+def _cur_stream(t):
+    return _stream_ptr(torch.cuda.current_stream(t.device))
+
+
+def _check_rows(name, t, inner):
+    if t.dtype != BF16 or t.dim() != 3 or t.shape[2] != inner or not t.is_contiguous() or not t.is_cuda:
+        raise ValueError(f"{name}: expected a contiguous CUDA bfloat16 [H, n, {inner}] tensor, got "
+                         f"{t.dtype} {tuple(t.shape)}")
+
+
+def fast_assign(x, centroids, out=None, **_tuning):
+    """Nearest centroid of every row, lowest index on ties (fast_assign.py:79-106).
+    x [H, N, 32], centroids [H, C, 32] bfloat16 -> labels [H, N] int32.  Tuning
+    keywords of the reference are accepted and ignored.  Distances are the
+    exact fp32 chains of the operator (the reference truncates the low 11 bits
+    of the distance in its packed key)."""
+    _check_rows("fast_assign x", x, 32)
+    _check_rows("fast_assign centroids", centroids, 32)
+    H, N, _ = x.shape
+    if centroids.shape[0] != H:
+        raise ValueError("fast_assign: head counts differ")
+    lib = _lib.load()
+    if out is None:
+        out = torch.empty(H, N, device=x.device, dtype=torch.int32)
+    ws = torch.empty(int(lib.t2t_assign_ws_bytes(H, N)), device=x.device, dtype=torch.uint8)
+    status = torch.zeros(1, device=x.device, dtype=torch.int32)
+    with torch.cuda.device(x.device):
+        check(lib.t2t_assign(ptr(x), ptr(centroids), ptr(out), H, N, centroids.shape[1], -1, 0, ptr(ws), ws.numel(),
+                             ptr(status), _cur_stream(x)), "t2t_assign")
+    return out
+
+
+def fast_gather(x, perm, out=None, **_tuning):
+    """o[h, i] = x[h, perm[h, i]] for x [H, N, 128] bfloat16 (fast_permute.py:54-56)."""
+    _check_rows("fast_gather x", x, 128)
+    H, N, _ = x.shape
+    perm_i = perm.to(torch.int32).contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(_lib.load().t2t_gather_rows(ptr(x), ptr(perm_i), ptr(out), H, N, _cur_stream(x)), "t2t_gather_rows")
+    return out
+
+
+def fused_update_vstats(ku, labels, old_centroids, v=None, **_tuning):
+    """Cluster means of ku under `labels`; an empty cluster keeps its old centroid
+    (fused_update_vstats.py:72-115).  Returns (new_centroids [H, C, 32] bfloat16,
+    counts [H, C] int32, None).  The means are the deterministic fixed-point ones
+    (the reference accumulates with fp32 atomics).  Only v=None is supported: the
+    operator computes value statistics inside t2t_kmeans_maintain."""
+    if v is not None:
+        raise NotImplementedError("fused_update_vstats: value statistics are part of t2t_kmeans_maintain here")
+    _check_rows("fused_update_vstats ku", ku, 32)
+    _check_rows("fused_update_vstats old_centroids", old_centroids, 32)
+    H, N, _ = ku.shape
+    Cn = old_centroids.shape[1]
+    lib = _lib.load()
+    lab = labels.to(torch.int32).contiguous()
+    newc = torch.empty_like(old_centroids)
+    counts = torch.empty(H, Cn, device=ku.device, dtype=torch.int32)
+    ws = torch.empty(int(lib.t2t_centroid_update_ws_bytes(H, N, Cn)), device=ku.device, dtype=torch.uint8)
+    with torch.cuda.device(ku.device):
+        check(lib.t2t_centroid_update(ptr(ku), ptr(lab), ptr(old_centroids), ptr(newc), ptr(counts), H, N, Cn,
+                                      ptr(ws), ws.numel(), _cur_stream(ku)), "t2t_centroid_update")
+    return newc, counts, None
+
+
 class MaskedStepDeploy:
     """Persistent buffers and kernels for one (H, N, C_Q) attention shape
     (deploy_step.py:152-242).
