@@ -39,3 +39,36 @@ def small_case():
     op = O.OracleOperator(H, N, CQ, s_frac=0.05)
     state = op.init_state(q, k)
     return dict(H=H, N=N, CQ=CQ, q=q, k=k, v=v, state=state)
+
+
+def run_gloo_ranks(worker, world, args=(), attempts=3, timeout=180):
+    """Spawn `world` CPU processes running worker(rank, world, port, queue, *args) and
+    collect one queue item per rank.  A rendezvous can fail when another process
+    grabs the port between probing and binding: the launch is retried on a fresh
+    port before the test gives up."""
+    import queue as _queue
+    import socket
+    import torch.multiprocessing as mp
+    last = None
+    for _ in range(attempts):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        procs = [ctx.Process(target=worker, args=(r, world, port, q, *args)) for r in range(world)]
+        for p in procs:
+            p.start()
+        items = []
+        try:
+            for _ in procs:
+                items.append(q.get(timeout=timeout))
+        except _queue.Empty as exc:
+            last = exc
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.terminate()
+        if len(items) == world:
+            return items
+    raise AssertionError(f"gloo ranks did not finish after {attempts} attempts: {last!r}")

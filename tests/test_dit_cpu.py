@@ -57,15 +57,8 @@ def test_sequence_sharded_step_equals_the_unsharded_step():
         x, text, 500.0, None)
     assert whole.shape == x.shape and bool(torch.isfinite(whole).all())
     assert (whole - x).abs().max() > 1e-3          # the step does something
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
-    for p in procs:
-        p.start()
-    parts = dict(q.get(timeout=180) for _ in procs)
-    for p in procs:
-        p.join(timeout=60)
+    from conftest import run_gloo_ranks
+    parts = dict(run_gloo_ranks(_worker, 2))
     got = torch.cat([parts[0], parts[1]])
     assert (got - whole).abs().max() <= 1e-4 * whole.abs().max()
 

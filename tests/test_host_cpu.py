@@ -106,7 +106,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _ulysses_worker(rank, world, port, N, H, D, q):
+def _ulysses_worker(rank, world, port, q, N, H, D):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
@@ -127,13 +127,6 @@ def _ulysses_worker(rank, world, port, N, H, D, q):
 
 @pytest.mark.parametrize("world", [2])
 def test_ulysses_all_to_all_round_trip_on_gloo(world):
-    ctx = mp.get_context("spawn")
-    q = ctx.Queue()
-    port = _free_port()
-    procs = [ctx.Process(target=_ulysses_worker, args=(r, world, port, 24, 4, 8, q)) for r in range(world)]
-    for p in procs:
-        p.start()
-    res = sorted(q.get(timeout=120) for _ in procs)
-    for p in procs:
-        p.join(timeout=60)
+    from conftest import run_gloo_ranks
+    res = sorted(run_gloo_ranks(_ulysses_worker, world, args=(24, 4, 8)))
     assert res == [(r, True) for r in range(world)]
