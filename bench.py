@@ -162,6 +162,26 @@ def cpu_head_step_factory(seed_head=0):
     return step, torch.get_num_threads()
 
 
+def cpu_small_config():
+    """The reference's CPU-runnable configuration on the host cores: one init_state and one rebuild call of
+    the oracle operator, and dense fp32 attention at the same shape."""
+    from oracle import t2t_oracle as O
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    O.FAST_DOT = True
+    H, N, CQ = 2, 4096, 32
+    q, k, v = locality_mixture(H, GRIDS["cpu"], dtype=torch.float32)
+    op = O.OracleOperator(H, N, CQ, s_frac=0.05, dtype=torch.float32)
+    t0 = time.perf_counter()
+    state = op.init_state(q, k)
+    t1 = time.perf_counter()
+    op.step(q, k, v, state)
+    t2 = time.perf_counter()
+    torch.nn.functional.scaled_dot_product_attention(q, k, v)
+    t3 = time.perf_counter()
+    return {"shape": "H 2, N 4096, CQ 32, fp32, 5 % budget", "init_state_ms": (t1 - t0) * 1e3,
+            "rebuild_step_ms": (t2 - t1) * 1e3, "dense_fp32_ms": (t3 - t2) * 1e3}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -409,6 +429,10 @@ def run_ours(args, rank, world, local_rank):
         val = step()
         cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                "sample": "one head of 40 (full 75,600 tokens), one rebuild call, time x 40"}
+        try:      # the CPU-sized configuration as a whole: H 2, N 4096, CQ 32, fp32, 5 % budget
+            cpu["cpu_config"] = cpu_small_config()
+        except Exception as exc:      # noqa: BLE001 - informative only
+            print(f"[bench] CPU configuration skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
 
     if rank == 0:
         amort = (ms_step + 7 * reuse_ms) / 8
