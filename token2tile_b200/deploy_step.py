@@ -395,6 +395,11 @@ class MaskedStepDeploy:
                 state["ck"] = ck16
                 state["cq"] = self._kmm_cq2.clone()
                 self._mark("kmeans")
+                # the key gather only needs kperm: it runs on the side stream, under the selection
+                # (one is bound by HBM, the other by integer arithmetic)
+                self.s_side.wait_stream(self.s_main)
+                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, _stream_ptr(self.s_side)),
+                      "t2t_gather_rows")
                 check(L.t2t_score_select_union(
                     ptr(self.QU), ptr(S["cks"]), ptr(S["counts"]), ptr(S["qperm"]), ptr(S["tile_sizes"]),
                     ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, ptr(self._ws),
@@ -404,7 +409,7 @@ class MaskedStepDeploy:
                 S["step"] = self._cfg_step
                 if publish:
                     self._cfg_hold[self._cfg_key] = S
-                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+                self.s_main.wait_stream(self.s_side)      # kp is ready
                 self._mark("gather_k")
                 check(L.t2t_tile_attn_plan(ptr(S["tile_sizes"]), ptr(S["counts"]), ptr(S["unip"]),
                                            ptr(S["tile_attn_plan"]), H, N, CQ, st), "t2t_tile_attn_plan")
