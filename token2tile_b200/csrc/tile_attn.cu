@@ -215,6 +215,62 @@ __device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
   }
 }
 
+// Runs of selected, non-empty key clusters of one union, as (first kp/vp row, first position in the
+// union) pairs in sRunStart / sRunCum (sRunCum[runs] = union length) and the run count in sMisc[1].
+// Called by every thread of the CTA (it contains two CTA-wide barriers); threads 0..127 hold 16 key
+// clusters each.  Returns false when the run list would not fit (the abort flag is then set).
+__device__ __forceinline__ bool build_runs(const int* __restrict__ koh, const uint32_t* __restrict__ ubr,
+                                           int* sRunStart, int* sRunCum, int* sMisc, volatile int* abort_flag,
+                                           int* status) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const bool scan = tid < 128;
+  const int c0 = scan ? tid * 16 : 0;
+  const uint32_t bw = scan ? (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu : 0u;
+  const int base0 = koh[c0];
+  bool pne0 = false;
+  if (scan && c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
+  int offs[17];
+  offs[0] = base0;
+#pragma unroll
+  for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
+  int cnt = 0, sz = 0;
+  {
+    bool pne = pne0;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+      if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
+      pne = cne;
+    }
+  }
+  // exclusive scans of (cnt, sz) over the 128 scanning threads
+  int* ws = sMisc + 8;
+  const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
+  if (scan && lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
+  __syncthreads();
+  int kbase = ic - cnt, pbase = is - sz;
+  for (int w = 0; w < warp && w < 4; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
+  const int totc = ws[0] + ws[1] + ws[2] + ws[3];
+  if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
+    if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
+  } else if (scan) {
+    bool pne = pne0;
+    int k = kbase, p = pbase;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
+      if (cne) {
+        if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
+        p += offs[j + 1] - offs[j];
+      }
+      pne = cne;
+    }
+    if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
+  }
+  __syncthreads();
+  return *abort_flag == 0;
+}
+
 // ---------------------------------------------------------------------------
 // exact attention over the unions
 // ---------------------------------------------------------------------------
@@ -303,55 +359,9 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     sQidx[tid] = h * N + qperm[rowbase + (tid < qrows ? tid : 0)];
 
     // ---- runs of selected, non-empty key clusters -----------------------------
-    {
-      const int* koh = pv.k_off + (size_t)h * (kC + 1);
-      const uint32_t* ubr = ub + ((size_t)h * CQ + qc) * (kC / 32);
-      const int c0 = tid * 16;
-      const uint32_t bw = (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu;
-      const int base0 = koh[c0];
-      bool pne0 = false;
-      if (c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
-      int offs[17];
-      offs[0] = base0;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
-      int cnt = 0, sz = 0;
-      {
-        bool pne = pne0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-          if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
-          pne = cne;
-        }
-      }
-      // 128-thread exclusive scans of (cnt, sz)
-      int* ws = sMisc + 8;
-      const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
-      if (lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
-      __syncthreads();
-      int kbase = ic - cnt, pbase = is - sz;
-      for (int w = 0; w < warp; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
-      const int totc = ws[0] + ws[1] + ws[2] + ws[3];
-      if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
-        if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
-      } else {
-        bool pne = pne0;
-        int k = kbase, p = pbase;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-          if (cne) {
-            if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
-            p += offs[j + 1] - offs[j];
-          }
-          pne = cne;
-        }
-        if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
-      }
-      __syncthreads();
-      if (*abort_flag) break;
-    }
+    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32), sRunStart, sRunCum, sMisc,
+                    abort_flag, status))
+      break;
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
 
@@ -687,56 +697,10 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       continue;
     }
 
-    // ---- runs of selected, non-empty key clusters (threads 0..127 hold 16 clusters each) ------
-    {
-      const int* koh = pv.k_off + (size_t)h * (kC + 1);
-      const uint32_t* ubr = ub + ((size_t)h * CQ + qc) * (kC / 32);
-      const bool scan = tid < 128;
-      const int c0 = scan ? tid * 16 : 0;
-      const uint32_t bw = scan ? (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu : 0u;
-      const int base0 = koh[c0];
-      bool pne0 = false;
-      if (scan && c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
-      int offs[17];
-      offs[0] = base0;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
-      int cnt = 0, sz = 0;
-      {
-        bool pne = pne0;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-          if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
-          pne = cne;
-        }
-      }
-      int* ws = sMisc + 8;
-      const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
-      if (scan && lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
-      __syncthreads();
-      int kbase = ic - cnt, pbase = is - sz;
-      for (int w = 0; w < warp && w < 4; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
-      const int totc = ws[0] + ws[1] + ws[2] + ws[3];
-      if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
-        if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
-      } else if (scan) {
-        bool pne = pne0;
-        int k = kbase, p = pbase;
-#pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-          if (cne) {
-            if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
-            p += offs[j + 1] - offs[j];
-          }
-          pne = cne;
-        }
-        if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
-      }
-      __syncthreads();
-      if (*abort_flag) break;
-    }
+    // ---- runs of selected, non-empty key clusters ------------------------------------------------
+    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32), sRunStart, sRunCum, sMisc,
+                    abort_flag, status))
+      break;
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
     const int rows0 = (qrows + 1) >> 1;                       // rows of group 0; group 1 takes the rest
