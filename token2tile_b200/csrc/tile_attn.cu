@@ -13,10 +13,14 @@
 //
 // One thread owns one query row (TMEM lane), so row maxima and sums need no
 // shuffles.  K/V rows of a union are contiguous runs in the cluster-major
-// copies kp/vp and are gathered with 16-byte cp.async into 128-byte-swizzled
-// tiles.  Two CTAs share an SM (256 TMEM columns each) so that the softmax of
-// one overlaps the MMAs and loads of the other.  Every mbarrier wait is
-// bounded; on a timeout the CTA raises a status word and leaves.
+// copies kp/vp; the attention kernels fetch them with TMA row gathers (four
+// rows per instruction) straight into 128-byte-swizzled tiles, the residual
+// kernel with 16-byte cp.async.  Tasks of up to 128 query rows run in
+// attn_kernel, two CTAs to an SM (256 TMEM columns each) so that the softmax
+// of one overlaps the MMAs and loads of the other; tasks of 129..256 rows run
+// in attn2_kernel, one warp-specialised CTA per SM whose two row groups share
+// one K/V stream.  Every mbarrier wait is bounded; on a timeout the CTA raises
+// a status word and leaves.
 #include <cuda.h>
 
 #include "common.cuh"
