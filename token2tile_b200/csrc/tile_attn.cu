@@ -893,16 +893,34 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
 // ---------------------------------------------------------------------------
 // centroid residual + merge, 128 sorted queries per CTA
 // ---------------------------------------------------------------------------
-constexpr int TL_Q = 128;
-constexpr int TL_C = 128;                 // centroids per tile
+constexpr int TL_Q = 128;                 // sorted queries per CTA (one softmax thread per row)
+constexpr int TL_H = 64;                  // centroids per step
+constexpr int TL_NH = kC / TL_H;          // steps per CTA
+constexpr int TL_STAGES = 3;              // ring depth of the centroid and value-sum tiles
 constexpr int TL_SQ = TL_Q * 128;         // 16 KB: QU rows padded to 128 B
-constexpr int TL_SC = TL_C * 128;         // 16 KB: cks rows padded to 128 B
-constexpr int TL_SV = TL_C * kD * 2;      // 32 KB
-constexpr int TL_SMEM_USED = TL_SQ + TL_SC + TL_SV + 64 + TL_C * 4 + 1024;
-// padded so that at most two CTAs share an SM: tensor memory holds two 256-column allocations
-constexpr int TL_SMEM = TL_SMEM_USED > 80 * 1024 ? TL_SMEM_USED : 80 * 1024;
+constexpr int TL_SC = TL_H * 128;         // 8 KB per stage: cks rows padded to 128 B
+constexpr int TL_SV = TL_H * kD * 2;      // 16 KB per stage
+constexpr int TL_OFF_C = TL_SQ;
+constexpr int TL_OFF_V = TL_OFF_C + TL_STAGES * TL_SC;
+constexpr int TL_OFF_CNT = TL_OFF_V + TL_STAGES * TL_SV;
+constexpr int TL_OFF_BAR = TL_OFF_CNT + kC * 4;
+// 97 KB: two CTAs share an SM, and no more than two (tensor memory holds two 256-column allocations)
+constexpr int TL_SMEM = TL_OFF_BAR + 64 + 1024;
+constexpr int TL_THREADS = 160;           // warps 0..3: one softmax thread per row; warp 4: the MMA lane
+static_assert(TL_NH % 2 == 0 && TL_NH >= 4, "the two score regions alternate");
+static_assert(3 * TL_SMEM > 227 * 1024, "at most two CTAs may share an SM");
 
-__global__ void __launch_bounds__(128, 2) tail_kernel(
+// Work is pipelined over steps of 64 centroids.  Tensor memory holds two 64-column score regions and the
+// 128-column accumulator T.  For step i (region b = i & 1):
+//   MMA lane      S_b = QU cks_i^T  ->  commit on sReady[b]
+//   softmax rows  wait sReady[b]; p = exp2(S_b - m) masked by the row's union, packed to bf16 into S_b;
+//                 arrive on pReady[b]
+//   MMA lane      wait pReady[b]; T += P_b sumv_i; S_b = QU cks_{i+2}^T; commit on sReady[b]
+// so the tensor work of one region runs under the softmax of the other.  The softmax threads also feed
+// the rings: at the start of step i they issue the cp.async copies of sumv_{i+1} and cks_{i+3} into the
+// stages that sReady[b] has just declared free, and before arriving on pReady[b] they wait for the copies
+// of the previous step (sumv_i, cks_{i+2}), which the MMA lane is about to read.
+__global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     const __nv_bfloat16* __restrict__ attn_out, const float* __restrict__ attn_lse,
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
     const __nv_bfloat16* __restrict__ sumv, const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
@@ -912,13 +930,15 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base, sC = base + TL_SQ, sV = base + TL_SQ + TL_SC;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + TL_SQ + TL_SC + TL_SV);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + TL_SQ + TL_SC + TL_SV + 16);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + TL_SQ + TL_SC + TL_SV + 32);
-  float* sCnt = reinterpret_cast<float*>(sm + TL_SQ + TL_SC + TL_SV + 64);
+  const uint32_t sQ = base, sC = base + TL_OFF_C, sV = base + TL_OFF_V;
+  float* sCnt = reinterpret_cast<float*>(sm + TL_OFF_CNT);
+  uint64_t* sReady = reinterpret_cast<uint64_t*>(sm + TL_OFF_BAR);        // [2], one arrival (tcgen05.commit)
+  uint64_t* pReady = sReady + 2;                                          // [2], 128 arrivals
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + TL_OFF_BAR + 32);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + TL_OFF_BAR + 48);
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool soft = warp < 4;
   const int h = blockIdx.y, qs = blockIdx.x * TL_Q;
   if (warp == 0) {
     tmem_alloc(tmem_slot, 256);
@@ -926,18 +946,40 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
   }
   if (tid == 0) {
     *abort_flag = 0;
-    mbar_init(bars + 0, 1);
-    mbar_init(bars + 1, 1);
+    mbar_init(sReady + 0, 1);
+    mbar_init(sReady + 1, 1);
+    mbar_init(pReady + 0, TL_Q);
+    mbar_init(pReady + 1, TL_Q);
     mbar_init_fence();
   }
   const int j = qs + tid;
-  const bool active = j < N;
+  const bool active = soft && j < N;
   const int orig = active ? qperm[(size_t)h * N + j] : 0;
   const int label = active ? qlab[(size_t)h * N + orig] : 0;
   const uint32_t* mrow = ub + ((size_t)h * CQ + label) * (kC / 32);
 
-  // QU rows of the 128 sorted queries: 64 B each, 4 chunks, into 128-byte rows
-  {
+  auto load_c = [&](int step) {   // centroid rows of one step: 64 rows x 64 B into 128-byte rows
+    const int ch = tid & 3, r0 = tid >> 2;
+    const __nv_bfloat16* src = cks + ((size_t)h * kC + step * TL_H) * kR + ch * 8;
+    const uint32_t dst = sC + (step % TL_STAGES) * TL_SC;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int r = r0 + 32 * u;
+      cp_async16(dst + sw128(r, ch), src + (size_t)r * kR, 16u);
+    }
+  };
+  auto load_v = [&](int step) {   // value sums of one step: 64 rows x 256 B as two 64-column blocks
+    const int ch = tid & 15, r0 = tid >> 4;
+    const __nv_bfloat16* src = sumv + ((size_t)h * kC + step * TL_H) * kD + ch * 8;
+    const uint32_t dst = sV + (step % TL_STAGES) * TL_SV + (ch >> 3) * (TL_H * 128);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int r = r0 + 8 * u;
+      cp_async16(dst + sw128(r, ch & 7), src + (size_t)r * kD, 16u);
+    }
+  };
+  if (soft) {
+    // group 0: QU rows of the 128 sorted queries (64 B each, 4 chunks) and the centroids of steps 0, 1
     const int ch = tid & 3, r0 = tid >> 2;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
@@ -946,183 +988,194 @@ __global__ void __launch_bounds__(128, 2) tail_kernel(
       const int o = valid ? qperm[(size_t)h * N + qs + r] : 0;
       cp_async16(sQ + sw128(r, ch), QU + ((size_t)h * N + o) * kR + ch * 8, valid ? 16u : 0u);
     }
+    load_c(0);
+    load_c(1);
     cp_async_commit();
+    // group 1: what the MMA lane reads after the first softmax
+    load_c(2);
+    load_v(0);
+    cp_async_commit();
+    for (int c = tid; c < kC; c += TL_Q) sCnt[c] = (float)ksz[(size_t)h * kC + c];
+    cp_async_wait<1>();
+    fence_proxy_async();
   }
-  auto load_c = [&](int tile) {   // centroid tile: 128 rows x 64 B
-    const int ch = tid & 3, r0 = tid >> 2;
-    const __nv_bfloat16* src = cks + ((size_t)h * kC + tile * TL_C) * kR + ch * 8;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int r = r0 + 32 * u;
-      cp_async16(sC + sw128(r, ch), src + (size_t)r * kR, 16u);
-    }
-    cp_async_commit();
-  };
-  auto load_v = [&](int tile) {   // value-sum tile: 128 rows x 256 B
-    const int ch = tid & 15, r0 = tid >> 4;
-    const __nv_bfloat16* src = sumv + ((size_t)h * kC + tile * TL_C) * kD + ch * 8;
-#pragma unroll
-    for (int u = 0; u < 16; ++u) {
-      const int r = r0 + 8 * u;
-      cp_async16(sV + (ch >> 3) * (TL_C * 128) + sw128(r, ch & 7), src + (size_t)r * kD, 16u);
-    }
-    cp_async_commit();
-  };
-  load_c(0);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
-  const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
-  constexpr uint32_t idescS = make_idesc_bf16(128, TL_C, false, false);
+  const uint32_t tS = tmem, tO = tmem + 2 * TL_H;
+  constexpr uint32_t idescS = make_idesc_bf16(128, TL_H, false, false);
   constexpr uint32_t idescT = make_idesc_bf16(128, kD, false, true);
   constexpr float LOG2E = 1.4426950408889634f;
-  constexpr int NT = kC / TL_C;
 
-  uint32_t phS = 0, phO = 0;
-  float m = -INFINITY, phi = 0.f;     // m in log2 units
-  bool any_tile = false;              // has any PV product been accumulated yet
+  auto issue_scores = [&](int step) {   // S_(step & 1) = QU cks_step^T, K = 32
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const uint64_t ad = make_sdesc(sQ + s * 32, 16, 1024);
+      const uint64_t bd = make_sdesc(sC + (step % TL_STAGES) * TL_SC + s * 32, 16, 1024);
+      umma_ss(tS + (step & 1) * TL_H, ad, bd, idescS, s > 0 ? 1u : 0u);
+    }
+  };
+
+  if (tid == TL_Q) {
+    // ---- MMA lane ----
+    issue_scores(0);
+    umma_commit(sReady + 0);
+    issue_scores(1);
+    umma_commit(sReady + 1);
+    for (int i = 0; i < TL_NH; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait(pReady + b, (i >> 1) & 1, abort_flag)) break;
+      tc_fence_after();
+      const uint32_t vb = sV + (i % TL_STAGES) * TL_SV;
+#pragma unroll
+      for (int s8 = 0; s8 < TL_H / 16; ++s8) {
+        const uint64_t bd = make_sdesc(vb + s8 * 2048, TL_H * 128, 1024);
+        umma_ts(tO, tS + b * TL_H + s8 * 8, bd, idescT, (i > 0 || s8 > 0) ? 1u : 0u);
+      }
+      if (i + 2 < TL_NH) issue_scores(i + 2);
+      umma_commit(sReady + b);
+    }
+  }
   bool dead = false;
-
-  for (int t = 0; t < NT; ++t) {
-    cp_async_wait<0>();
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
+  if (soft) {
+    // ---- softmax rows ----
+    const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
+    float m = -INFINITY, phi = 0.f;     // m in log2 units
+    uint2 mw_next = *reinterpret_cast<const uint2*>(mrow);   // union bits of the step's 64 centroids
+    for (int i = 0; i < TL_NH; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait(sReady + b, (i >> 1) & 1, abort_flag)) { dead = true; break; }
       tc_fence_after();
+      // the stages of sumv_{i-2} and cks_i are free now
+      if (i + 1 < TL_NH) load_v(i + 1);
+      if (i + 3 < TL_NH) load_c(i + 3);
+      cp_async_commit();
+      const uint2 mw2 = mw_next;
+      if (i + 1 < TL_NH) mw_next = *reinterpret_cast<const uint2*>(mrow + (i + 1) * 2);
+      float s[TL_H];
 #pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const uint64_t ad = make_sdesc(sQ + s * 32, 16, 1024);
-        const uint64_t bd = make_sdesc(sC + s * 32, 16, 1024);
-        umma_ss(tS, ad, bd, idescS, s > 0 ? 1u : 0u);
+      for (int c = 0; c < TL_H / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tS_lane + b * TL_H + c * 32, v);
+        tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 32; ++k) s[c * 32 + k] = __uint_as_float(v[k]);
       }
-      umma_commit(bars + 0);
+      // The scores are rounded to fp16 exactly as the selection saw them, and the members of the row's union
+      // become -inf, both on packed pairs: shifting a word of union bits left by 7 - r puts the bits of the
+      // centroids r, r + 8, r + 16, r + 24 on the sign bits of its four bytes, and a byte permute with sign
+      // replication turns two such bytes into the select mask of a pair.  The scores stay in natural-log
+      // units here; log2(e) is folded into the exponent's multiply-add below.
+      const uint32_t mw[2] = {mw2.x, mw2.y};
+      uint32_t sh[2][8];
+#pragma unroll
+      for (int w = 0; w < 2; ++w)
+#pragma unroll
+        for (int r = 0; r < 8; ++r) sh[w][r] = mw[w] << (7 - r);
+      __half2 hm[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) hm[a] = __float2half2_rn(-INFINITY);
+#pragma unroll
+      for (int k = 0; k < TL_H; k += 2) {
+        const int w = k >> 5, r = k & 7, jb = (k & 31) >> 3;
+        const uint32_t sel = (8u | jb) * 0x11u | ((8u | (4u + jb)) * 0x11u) << 8;
+        uint32_t msk;   // selector bit 3 of a nibble: replicate the chosen byte's sign over the result byte
+        asm("prmt.b32 %0, %1, %2, %3;" : "=r"(msk) : "r"(sh[w][r]), "r"(sh[w][r + 1]), "r"(sel));
+        const __half2 h2 = __floats2half2_rn(s[k], s[k + 1]);
+        const uint32_t u = (*reinterpret_cast<const uint32_t*>(&h2) & ~msk) | (0xFC00FC00u & msk);
+        const __half2 hq = *reinterpret_cast<const __half2*>(&u);
+        hm[(k >> 1) & 3] = __hmax2(hm[(k >> 1) & 3], hq);
+        const float2 g = __half22float2(hq);
+        s[k] = g.x;
+        s[k + 1] = g.y;
+      }
+      const float2 mxp = __half22float2(__hmax2(__hmax2(hm[0], hm[1]), __hmax2(hm[2], hm[3])));
+      const float mx = fmaxf(mxp.x, mxp.y) * LOG2E;
+      const bool grow = mx > m + kLazy || (m == -INFINITY && mx > -INFINITY);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float mnew = grow ? mx : m;
+        const float alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mnew);
+        if (i > 0) {
+          // T is rescaled in place: the product of step i - 1 may still be running, its commit is the
+          // next completion of the other region's barrier (the same one step i + 1 waits for)
+          if (!mbar_wait(sReady + (b ^ 1), (((i - 1) >> 1) + 1) & 1, abort_flag)) { dead = true; break; }
+          tc_fence_after();
+          rescale_rows(tO_lane, alpha);
+        }
+        phi *= alpha;
+        m = mnew;
+      }
+      const float nm = (m == -INFINITY) ? 0.f : -m;
+      const float4* cnt4 = reinterpret_cast<const float4*>(sCnt + i * TL_H);
+      float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[TL_H / 2];
+#pragma unroll
+      for (int k = 0; k < TL_H / 4; ++k) {
+        const float4 cn = cnt4[k];
+        const float p0 = ex2_approx(fmaf(s[4 * k], LOG2E, nm));
+        const float p1 = ex2_approx(fmaf(s[4 * k + 1], LOG2E, nm));
+        const float p2 = ex2_approx(fmaf(s[4 * k + 2], LOG2E, nm));
+        const float p3 = ex2_approx(fmaf(s[4 * k + 3], LOG2E, nm));
+        ps4[k & 3] = fmaf(p1, cn.y, fmaf(p0, cn.x, ps4[k & 3]));
+        ps4[(k + 2) & 3] = fmaf(p3, cn.w, fmaf(p2, cn.z, ps4[(k + 2) & 3]));
+        pk[2 * k] = pack_bf2(p0, p1);
+        pk[2 * k + 1] = pack_bf2(p2, p3);
+      }
+      phi += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+      tmem_st32(tS_lane + b * TL_H, pk);
+      tmem_wait_st();
+      // sumv_i and cks_{i+2} (issued one step ago) must have landed before the MMA lane reads them
+      cp_async_wait<1>();
+      fence_proxy_async();
+      tc_fence_before();
+      mbar_arrive(pReady + b);
     }
-    sCnt[tid] = (float)ksz[(size_t)h * kC + t * TL_C + tid];
-    const uint4 mw4 = *reinterpret_cast<const uint4*>(mrow + t * 4);
-    if (!mbar_wait(bars + 0, phS, abort_flag)) { dead = true; break; }
-    phS ^= 1u;
-    if (t > 0) {
-      if (!mbar_wait(bars + 1, phO, abort_flag)) { dead = true; break; }
-      phO ^= 1u;
-    }
+    // the last commit on each region's barrier covers every product
+    if (!dead) dead = !mbar_wait(sReady + 0, (TL_NH >> 1) & 1, abort_flag);
+    if (!dead) dead = !mbar_wait(sReady + 1, (TL_NH >> 1) & 1, abort_flag);
     tc_fence_after();
-    load_v(t);
-    const bool more = t + 1 < NT;
-    if (more) load_c(t + 1);
-    __syncthreads();     // sCnt visible
-
-    float s[TL_C];
+    if (!dead) {
+      // merge with the exact part (natural-log units from here on); rows past N
+      // only take part in the warp-collective TMEM loads
+      const float lam = lam_s[h], tw = *tailw_ptr;
+      const float mt = (m == -INFINITY) ? 0.f : m * 0.6931471805599453f;
+      const float le = active ? attn_lse[(size_t)h * N + j] : 0.f;
+      float ex, st;
+      if (le >= mt) { ex = 1.0f; st = __expf(mt - le); } else { ex = __expf(le - mt); st = 1.0f; }
+      const float ph = st * phi;
+      const bool bad = ph <= 1.0e-6f * ex;
+      const float inv = 1.0f / fmaxf(ex + ph * tw, 1.0e-12f);
+      const float we = bad ? 1.0f : ex * inv;
+      const float wt = bad ? 0.0f : st * tw * lam * inv;
+      const uint4* src = reinterpret_cast<const uint4*>(attn_out + ((size_t)h * N + (active ? j : 0)) * kD);
+      uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)h * N + orig) * kD);
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32];
-      tmem_ld32(tS_lane + c * 32, v);
-      tmem_wait_ld();
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld32(tO_lane + c * 32, v);
+        tmem_wait_ld();
+        if (active) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(v[i]);
-    }
-    const uint32_t mw[4] = {mw4.x, mw4.y, mw4.z, mw4.w};
-    float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-    for (int i = 0; i < TL_C; i += 2) {
-      // the scores are rounded to fp16 exactly as the selection saw them (one packed conversion per pair);
-      // they stay in natural-log units here, log2(e) is folded into the exponent's multiply-add below
-      const __half2 h2 = __floats2half2_rn(s[i], s[i + 1]);
-      const float2 g = __half22float2(h2);
-      s[i] = ((mw[i >> 5] >> (i & 31)) & 1u) ? -INFINITY : g.x;
-      s[i + 1] = ((mw[(i + 1) >> 5] >> ((i + 1) & 31)) & 1u) ? -INFINITY : g.y;
-      mx4[(i >> 1) & 3] = fmaxf(mx4[(i >> 1) & 3], fmaxf(s[i], s[i + 1]));
-    }
-    const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * LOG2E;
-    const bool grow = mx > m + kLazy || (m == -INFINITY && mx > -INFINITY);
-    if (__any_sync(0xffffffffu, grow)) {
-      const float mnew = grow ? mx : m;
-      const float alpha = (m == -INFINITY) ? 0.f : ex2_approx(m - mnew);
-      if (any_tile) rescale_rows(tO_lane, alpha);
-      phi *= alpha;
-      m = mnew;
-    }
-    const float nm = (m == -INFINITY) ? 0.f : -m;
-    float ps4[4] = {0.f, 0.f, 0.f, 0.f};
-    uint32_t pk[TL_C / 2];
-#pragma unroll
-    for (int i = 0; i < TL_C / 2; ++i) {
-      const float p0 = ex2_approx(fmaf(s[2 * i], LOG2E, nm));
-      const float p1 = ex2_approx(fmaf(s[2 * i + 1], LOG2E, nm));
-      ps4[i & 3] = fmaf(p1, sCnt[2 * i + 1], fmaf(p0, sCnt[2 * i], ps4[i & 3]));
-      pk[i] = pack_bf2(p0, p1);
-    }
-    const float ps = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
-    phi += ps;
-    {
-      uint32_t lo[32], hi[32];
-#pragma unroll
-      for (int i = 0; i < 32; ++i) { lo[i] = pk[i]; hi[i] = pk[32 + i]; }
-      tmem_st32(tS_lane, lo);
-      tmem_st32(tS_lane + 32, hi);
-    }
-    tmem_wait_st();
-    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-#pragma unroll
-      for (int s8 = 0; s8 < 8; ++s8) {
-        const uint64_t bd = make_sdesc(sV + s8 * 2048, TL_C * 128, 1024);
-        umma_ts(tO, tS + s8 * 8, bd, idescT, (t > 0 || s8 > 0) ? 1u : 0u);
-      }
-      umma_commit(bars + 1);
-    }
-    any_tile = true;
-  }
-  if (!dead) {
-    if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
-  }
-  tc_fence_after();
-  if (!dead) {
-    // merge with the exact part (natural-log units from here on); rows past N
-    // only take part in the warp-collective TMEM loads
-    const float lam = lam_s[h], tw = *tailw_ptr;
-    const float mt = (m == -INFINITY) ? 0.f : m * 0.6931471805599453f;
-    const float le = active ? attn_lse[(size_t)h * N + j] : 0.f;
-    float ex, st;
-    if (le >= mt) { ex = 1.0f; st = __expf(mt - le); } else { ex = __expf(le - mt); st = 1.0f; }
-    const float ph = st * phi;
-    const bool bad = ph <= 1.0e-6f * ex;
-    const float inv = 1.0f / fmaxf(ex + ph * tw, 1.0e-12f);
-    const float we = bad ? 1.0f : ex * inv;
-    const float wt = bad ? 0.0f : st * tw * lam * inv;
-    const uint4* src = reinterpret_cast<const uint4*>(attn_out + ((size_t)h * N + (active ? j : 0)) * kD);
-    uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)h * N + orig) * kD);
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint32_t v[32];
-      tmem_ld32(tO_lane + c * 32, v);
-      tmem_wait_ld();
-      if (active) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const uint4 e = src[c * 4 + g];
-          uint4 o;
-          if (bad) {
-            o = e;
-          } else {
-            o.x = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 0]), we * bf_lo(e.x)), fmaf(wt, __uint_as_float(v[8 * g + 1]), we * bf_hi(e.x)));
-            o.y = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 2]), we * bf_lo(e.y)), fmaf(wt, __uint_as_float(v[8 * g + 3]), we * bf_hi(e.y)));
-            o.z = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 4]), we * bf_lo(e.z)), fmaf(wt, __uint_as_float(v[8 * g + 5]), we * bf_hi(e.z)));
-            o.w = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 6]), we * bf_lo(e.w)), fmaf(wt, __uint_as_float(v[8 * g + 7]), we * bf_hi(e.w)));
+          for (int g = 0; g < 4; ++g) {
+            const uint4 e = src[c * 4 + g];
+            uint4 o;
+            if (bad) {
+              o = e;
+            } else {
+              o.x = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 0]), we * bf_lo(e.x)), fmaf(wt, __uint_as_float(v[8 * g + 1]), we * bf_hi(e.x)));
+              o.y = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 2]), we * bf_lo(e.y)), fmaf(wt, __uint_as_float(v[8 * g + 3]), we * bf_hi(e.y)));
+              o.z = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 4]), we * bf_lo(e.z)), fmaf(wt, __uint_as_float(v[8 * g + 5]), we * bf_hi(e.z)));
+              o.w = pack_bf2(fmaf(wt, __uint_as_float(v[8 * g + 6]), we * bf_lo(e.w)), fmaf(wt, __uint_as_float(v[8 * g + 7]), we * bf_hi(e.w)));
+            }
+            dst[c * 4 + g] = o;
           }
-          dst[c * 4 + g] = o;
         }
       }
     }
+    cp_async_wait<0>();
   }
-  if (dead && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
-  cp_async_wait<0>();
+  if (*abort_flag && (tid & 31) == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
@@ -1202,7 +1255,7 @@ extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* 
   split_ws(ws, H, N, &attn_out, &attn_lse);
   if (cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
-  tail_kernel<<<dim3(cdiv(N, TL_Q), H), 128, TL_SMEM, st>>>(
+  tail_kernel<<<dim3(cdiv(N, TL_Q), H), TL_THREADS, TL_SMEM, st>>>(
       attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const __nv_bfloat16*)sumv,
       (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
       (__nv_bfloat16*)out, N, CQ, d_status);
