@@ -979,24 +979,32 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     }
   };
   if (soft) {
-    // group 0: QU rows of the 128 sorted queries (64 B each, 4 chunks) and the centroids of steps 0, 1
-    const int ch = tid & 3, r0 = tid >> 2;
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int r = r0 + 32 * u;
-      const bool valid = qs + r < N;
-      const int o = valid ? qperm[(size_t)h * N + qs + r] : 0;
-      cp_async16(sQ + sw128(r, ch), QU + ((size_t)h * N + o) * kR + ch * 8, valid ? 16u : 0u);
-    }
+    // group 0: the copies that depend on nothing (centroids of steps 0..2, value sums of step 0) go first
     load_c(0);
     load_c(1);
-    cp_async_commit();
-    // group 1: what the MMA lane reads after the first softmax
     load_c(2);
     load_v(0);
     cp_async_commit();
-    for (int c = tid; c < kC; c += TL_Q) sCnt[c] = (float)ksz[(size_t)h * kC + c];
-    cp_async_wait<1>();
+    // group 1: QU rows of the 128 sorted queries (64 B each, 4 chunks), behind the loads of their indices
+    const int ch = tid & 3, r0 = tid >> 2;
+    int o4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) o4[u] = qs + r0 + 32 * u < N ? qperm[(size_t)h * N + qs + r0 + 32 * u] : -1;
+    const int4* ksz4 = reinterpret_cast<const int4*>(ksz + (size_t)h * kC);
+    int4 kz[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) kz[u] = ksz4[tid + TL_Q * u];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int r = r0 + 32 * u;
+      cp_async16(sQ + sw128(r, ch), QU + ((size_t)h * N + max(o4[u], 0)) * kR + ch * 8, o4[u] >= 0 ? 16u : 0u);
+    }
+    cp_async_commit();
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      reinterpret_cast<float4*>(sCnt)[tid + TL_Q * u] =
+          make_float4((float)kz[u].x, (float)kz[u].y, (float)kz[u].z, (float)kz[u].w);
+    cp_async_wait<0>();
     fence_proxy_async();
   }
   tc_fence_before();
@@ -1131,6 +1139,13 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       tc_fence_before();
       mbar_arrive(pReady + b);
     }
+    // the row of the exact part is fetched while the last products finish
+    const uint4* src = reinterpret_cast<const uint4*>(attn_out + ((size_t)h * N + (active ? j : 0)) * kD);
+    uint4 ex16[16];
+#pragma unroll
+    for (int g = 0; g < 16; ++g) ex16[g] = ldg_nc_v4(src + g);
+    const float lam = lam_s[h], tw = *tailw_ptr;
+    const float le = active ? attn_lse[(size_t)h * N + j] : 0.f;
     // the last commit on each region's barrier covers every product
     if (!dead) dead = !mbar_wait(sReady + 0, (TL_NH >> 1) & 1, abort_flag);
     if (!dead) dead = !mbar_wait(sReady + 1, (TL_NH >> 1) & 1, abort_flag);
@@ -1138,9 +1153,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     if (!dead) {
       // merge with the exact part (natural-log units from here on); rows past N
       // only take part in the warp-collective TMEM loads
-      const float lam = lam_s[h], tw = *tailw_ptr;
       const float mt = (m == -INFINITY) ? 0.f : m * 0.6931471805599453f;
-      const float le = active ? attn_lse[(size_t)h * N + j] : 0.f;
       float ex, st;
       if (le >= mt) { ex = 1.0f; st = __expf(mt - le); } else { ex = __expf(le - mt); st = 1.0f; }
       const float ph = st * phi;
@@ -1148,7 +1161,6 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       const float inv = 1.0f / fmaxf(ex + ph * tw, 1.0e-12f);
       const float we = bad ? 1.0f : ex * inv;
       const float wt = bad ? 0.0f : st * tw * lam * inv;
-      const uint4* src = reinterpret_cast<const uint4*>(attn_out + ((size_t)h * N + (active ? j : 0)) * kD);
       uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)h * N + orig) * kD);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -1158,7 +1170,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
         if (active) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const uint4 e = src[c * 4 + g];
+            const uint4 e = ex16[c * 4 + g];
             uint4 o;
             if (bad) {
               o = e;
