@@ -127,6 +127,17 @@ __device__ __forceinline__ void tma_gather4(uint32_t dst, const void* map, int c
       : "memory");
 }
 
+// A (box columns) x (box rows) tile of a 2D tensor, starting at column `col` and row `row`, lands as
+// consecutive 128-byte rows of a SWIZZLE_128B shared-memory tile (`dst` 1024-byte aligned); completion is
+// counted in bytes on `bar`.  `col` x element size must be a multiple of 16 bytes.  No multicast.
+__device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* map, int col, int row, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(row), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");

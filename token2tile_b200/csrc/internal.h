@@ -24,5 +24,7 @@ int launch_select_fix(const __nv_bfloat16* QU, const __nv_bfloat16* cks, const i
 // with a 64-column x 1-row box and 128-byte swizzle, for tma_gather4 (tma_rows.cu).
 // False when the driver entry point is missing or the encoding is refused.
 bool make_row_gather_map(void* map_out, const void* base, uint64_t rows);
+// Same matrix, box of 64 columns x `box_rows` rows: plain tile loads of contiguous rows.
+bool make_row_tile_map(void* map_out, const void* base, uint64_t rows, uint32_t box_rows);
 
 }  // namespace t2t

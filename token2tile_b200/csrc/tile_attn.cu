@@ -905,7 +905,7 @@ constexpr int TL_OFF_V = TL_OFF_C + TL_STAGES * TL_SC;
 constexpr int TL_OFF_CNT = TL_OFF_V + TL_STAGES * TL_SV;
 constexpr int TL_OFF_BAR = TL_OFF_CNT + kC * 4;
 // 97 KB: two CTAs share an SM, and no more than two (tensor memory holds two 256-column allocations)
-constexpr int TL_SMEM = TL_OFF_BAR + 64 + 1024;
+constexpr int TL_SMEM = TL_OFF_BAR + 128 + 1024;
 constexpr int TL_THREADS = 160;           // warps 0..3: one softmax thread per row; warp 4: the MMA lane
 static_assert(TL_NH % 2 == 0 && TL_NH >= 4, "the two score regions alternate");
 static_assert(3 * TL_SMEM > 227 * 1024, "at most two CTAs may share an SM");
@@ -921,9 +921,9 @@ static_assert(3 * TL_SMEM > 227 * 1024, "at most two CTAs may share an SM");
 // stages that sReady[b] has just declared free, and before arriving on pReady[b] they wait for the copies
 // of the previous step (sumv_i, cks_{i+2}), which the MMA lane is about to read.
 __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
-    const __nv_bfloat16* __restrict__ attn_out, const float* __restrict__ attn_lse,
+    const __grid_constant__ CUtensorMap mapSumv, const __nv_bfloat16* __restrict__ attn_out, const float* __restrict__ attn_lse,
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
-    const __nv_bfloat16* __restrict__ sumv, const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
+    const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
     const int* __restrict__ qlab, const int* __restrict__ qperm, const float* __restrict__ lam_s,
     const float* __restrict__ tailw_ptr, __nv_bfloat16* __restrict__ out, int N, int CQ,
     int* __restrict__ status) {
@@ -934,8 +934,9 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
   float* sCnt = reinterpret_cast<float*>(sm + TL_OFF_CNT);
   uint64_t* sReady = reinterpret_cast<uint64_t*>(sm + TL_OFF_BAR);        // [2], one arrival (tcgen05.commit)
   uint64_t* pReady = sReady + 2;                                          // [2], 128 arrivals
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + TL_OFF_BAR + 32);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + TL_OFF_BAR + 48);
+  uint64_t* vFull = sReady + 4;                                           // [TL_STAGES], bytes of one value-sum tile
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + TL_OFF_BAR + 64);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + TL_OFF_BAR + 80);
 
   const int tid = threadIdx.x, warp = tid >> 5;
   const bool soft = warp < 4;
@@ -950,6 +951,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     mbar_init(sReady + 1, 1);
     mbar_init(pReady + 0, TL_Q);
     mbar_init(pReady + 1, TL_Q);
+    for (int st = 0; st < TL_STAGES; ++st) mbar_init(vFull + st, 1);
     mbar_init_fence();
   }
   const int j = qs + tid;
@@ -968,22 +970,11 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       cp_async16(dst + sw128(r, ch), src + (size_t)r * kR, 16u);
     }
   };
-  auto load_v = [&](int step) {   // value sums of one step: 64 rows x 256 B as two 64-column blocks
-    const int ch = tid & 15, r0 = tid >> 4;
-    const __nv_bfloat16* src = sumv + ((size_t)h * kC + step * TL_H) * kD + ch * 8;
-    const uint32_t dst = sV + (step % TL_STAGES) * TL_SV + (ch >> 3) * (TL_H * 128);
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {
-      const int r = r0 + 8 * u;
-      cp_async16(dst + sw128(r, ch & 7), src + (size_t)r * kD, 16u);
-    }
-  };
   if (soft) {
-    // group 0: the copies that depend on nothing (centroids of steps 0..2, value sums of step 0) go first
+    // group 0: the copies that depend on nothing (centroids of steps 0..2) go first
     load_c(0);
     load_c(1);
     load_c(2);
-    load_v(0);
     cp_async_commit();
     // group 1: QU rows of the 128 sorted queries (64 B each, 4 chunks), behind the loads of their indices
     const int ch = tid & 3, r0 = tid >> 2;
@@ -1025,8 +1016,17 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     }
   };
 
+  // value sums of one step: 64 rows x 256 B as two 64-column blocks, one TMA tile load each
+  auto load_v = [&](int step) {
+    uint64_t* bar = vFull + step % TL_STAGES;
+    const uint32_t dst = sV + (step % TL_STAGES) * TL_SV;
+    mbar_arrive_expect_tx(bar, TL_SV);
+    tma_load_tile(dst, &mapSumv, 0, h * kC + step * TL_H, bar);
+    tma_load_tile(dst + TL_H * 128, &mapSumv, 64, h * kC + step * TL_H, bar);
+  };
   if (tid == TL_Q) {
     // ---- MMA lane ----
+    load_v(0);
     issue_scores(0);
     umma_commit(sReady + 0);
     issue_scores(1);
@@ -1035,6 +1035,9 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       const int b = i & 1;
       if (!mbar_wait(pReady + b, (i >> 1) & 1, abort_flag)) break;
       tc_fence_after();
+      // every softmax thread has seen the commit behind the product of step i - 2: its stage is free
+      if (i + 1 < TL_NH) load_v(i + 1);
+      if (!mbar_wait(vFull + i % TL_STAGES, (i / TL_STAGES) & 1, abort_flag)) break;
       const uint32_t vb = sV + (i % TL_STAGES) * TL_SV;
 #pragma unroll
       for (int s8 = 0; s8 < TL_H / 16; ++s8) {
@@ -1055,8 +1058,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       const int b = i & 1;
       if (!mbar_wait(sReady + b, (i >> 1) & 1, abort_flag)) { dead = true; break; }
       tc_fence_after();
-      // the stages of sumv_{i-2} and cks_i are free now
-      if (i + 1 < TL_NH) load_v(i + 1);
+      // the stage of cks_i is free now
       if (i + 3 < TL_NH) load_c(i + 3);
       cp_async_commit();
       const uint2 mw2 = mw_next;
@@ -1133,7 +1135,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       phi += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
       tmem_st32(tS_lane + b * TL_H, pk);
       tmem_wait_st();
-      // sumv_i and cks_{i+2} (issued one step ago) must have landed before the MMA lane reads them
+      // cks_{i+2} (issued one step ago) must have landed before the MMA lane reads it
       cp_async_wait<1>();
       fence_proxy_async();
       tc_fence_before();
@@ -1267,9 +1269,11 @@ extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* 
   split_ws(ws, H, N, &attn_out, &attn_lse);
   if (cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
+  // the value sums as an [H * 2048, 128] matrix, fetched 64 rows x 64 columns at a time
+  CUtensorMap msv;
+  if (!make_row_tile_map(&msv, sumv, (uint64_t)H * kC, TL_H)) return T2T_ERR_CUDA;
   tail_kernel<<<dim3(cdiv(N, TL_Q), H), TL_THREADS, TL_SMEM, st>>>(
-      attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const __nv_bfloat16*)sumv,
-      (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
+      msv, attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
       (__nv_bfloat16*)out, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }

@@ -28,16 +28,20 @@ static EncodeTiledFn encode_tiled() {
   return fn;
 }
 
-bool make_row_gather_map(void* map_out, const void* base, uint64_t rows) {
+bool make_row_tile_map(void* map_out, const void* base, uint64_t rows, uint32_t box_rows) {
   EncodeTiledFn fn = encode_tiled();
-  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15u)) return false;
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15u) || box_rows == 0 || box_rows > 256) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)kD, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)kD * 2};
-  const cuuint32_t box[2] = {64, 1};
+  const cuuint32_t box[2] = {64, box_rows};
   const cuuint32_t elem[2] = {1, 1};
   return fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base),
             dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+bool make_row_gather_map(void* map_out, const void* base, uint64_t rows) {
+  return make_row_tile_map(map_out, base, rows, 1);
 }
 
 // One 128-row tile gathered by 64 instructions (two 64-column blocks x 32 groups of
