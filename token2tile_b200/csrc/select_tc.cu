@@ -39,6 +39,8 @@ constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
 constexpr int ST_MAX_ITERS = 5;
 constexpr int kMomFloats = 32 + 32 * 32;   // per head: mean centroid, second-moment matrix
+constexpr int ST_TPC = 4;                  // consecutive 128-row tiles of one head per CTA: the head's centroids, sizes
+                                           // and prefix sums are staged once for all of them
 constexpr int ST_STRAGGLERS = 8;           // this few unsettled rows of a tile go to the exact kernel instead of another pass
 
 constexpr int OFF_CK = 0;                               // 1024 rows x 128 B: centroid c in row c % 1024, half c / 1024
@@ -101,8 +103,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   const int g = tid >> 7;            // column group: chunks g, g + 4, g + 8, ...
   const int r = tid & 127;           // row of the tile = TMEM lane
   const int h = blockIdx.y;
-  const int p0 = blockIdx.x * 128;                      // first sorted row of this tile
-  const int rows_here = min(128, N - p0);
   const __nv_bfloat16* ckh = cks + (size_t)h * kC * kR;
 
   if (warp == 0) {
@@ -218,7 +218,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     wg_sync(g);
   };
 
-  {
+#pragma unroll 1
+  for (int ti = 0; ti < ST_TPC; ++ti) {
+    const int p0 = (blockIdx.x * ST_TPC + ti) * 128;    // first sorted row of this tile
+    if (p0 >= N || dead) break;
+    const int rows_here = min(128, N - p0);
     {
       const int ar = tid >> 2, ch = tid & 3;
       const bool valid = ar < rows_here;
@@ -592,13 +596,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         qh[2 + 2 * slot] = sRowI[R_CLU * 128 + r] | ((st - RS_QUEUE) << 24);      // the reason rides in the top byte
       }
     }
-  }
-  __syncthreads();
-  {
-    // segment bitmaps -> the (zero-initialised) bitmaps of their query clusters
-    const int k = tid >> 6, w = tid & 63;
-    const uint32_t bits = sUnion[tid];
-    if (k < *sNseg && bits) atomicOr(reinterpret_cast<unsigned*>(unip) + ((size_t)h * CQ + sSegClu[k]) * 64 + w, bits);
+    __syncthreads();
+    {
+      // segment bitmaps -> the (zero-initialised) bitmaps of their query clusters
+      const int k = tid >> 6, w = tid & 63;
+      const uint32_t bits = sUnion[tid];
+      if (k < *sNseg && bits)
+        atomicOr(reinterpret_cast<unsigned*>(unip) + ((size_t)h * CQ + sSegClu[k]) * 64 + w, bits);
+      sUnion[tid] = 0u;      // each thread clears the word it has just flushed, for the next tile
+    }
+    __syncthreads();
   }
   if (*abort_flag && tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
   tc_fence_before();
@@ -657,7 +664,7 @@ extern "C" int t2t_score_select_union(const void* QU, const void* cks, const voi
     return T2T_ERR_CUDA;
   if (cudaFuncSetAttribute(select_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ST_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
-  select_tc_kernel<<<dim3(cdiv(N, 128), H), ST_THREADS, ST_SMEM, st>>>(
+  select_tc_kernel<<<dim3(cdiv(cdiv(N, 128), ST_TPC), H), ST_THREADS, ST_SMEM, st>>>(
       (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const int*)qperm,
       (const int*)tile_sizes, ns, (int*)unip, (int*)rowcnt, N, CQ, fixq, mom, d_status);
   if (pin_tail > 0) pin_bit_kernel<<<cdiv(H * CQ, 256), 256, 0, st>>>((int*)unip, H * CQ);
