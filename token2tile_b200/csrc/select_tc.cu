@@ -55,12 +55,14 @@ constexpr int ST_MAXCQ = 2048;                          // prefix sums of the qu
 constexpr int OFF_UNION = OFF_ROW + 17 * 128 * 4;       // [ST_MAXSEG][64] segment bitmaps
 constexpr int OFF_PRE = OFF_UNION + ST_MAXSEG * 64 * 4; // [ST_MAXCQ + 1] first sorted row of every query cluster
 constexpr int OFF_MISC = OFF_PRE + (ST_MAXCQ + 4) * 4;  // barriers, segment tables, ...
-constexpr int ST_SMEM = OFF_MISC + 512 + 1024;
+constexpr int OFF_MOM = OFF_MISC + 512;                 // [kMomFloats] the head's centroid moments
+constexpr int ST_SMEM = OFF_MOM + kMomFloats * 4 + 1024;
+static_assert(ST_SMEM <= 227 * 1024, "shared memory of select_tc_kernel");
 
 // RS_QUEUE + k: queued for the exact kernel; k says why (1 non-finite scores, 2 threshold not bracketed,
 // 3 too many candidates, 4 budget met above the window, 5 / 6 threshold outside the window, 7 walk ran dry,
 // 8 the tile spans more query clusters than it has segment bitmaps)
-enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3 };
+enum : int { RS_SEARCH = 0, RS_COLLECT = 1, RS_DONE = 2, RS_QUEUE = 3, RS_WALK = 16 };
 // per-row scalar slots
 enum : int { R_LO = 0, R_HI, R_INV, R_THRA, R_THRW, R_EPS, R_MIN, R_CUM, R_STATE, R_NCAND, R_SIZEA, R_ORIG, R_E2, R_CLU, R_SEG, R_OVF, R_MAX };
 
@@ -70,6 +72,10 @@ __device__ __forceinline__ int key16_from_half(__half hv) {
   return (int)((u ^ 0x8000u) & 0xFFFFu);
 }
 __device__ __forceinline__ int key16_from_score(float s) { return key16_from_half(__float2half_rn(s)); }
+
+// Candidate slot `slot` of row r: the slot index is rotated by the row so that the rows of a warp, reading the
+// same slot, hit 32 different banks (the row stride, ST_CAP words, is a multiple of the bank count).
+__device__ __forceinline__ int cand_at(int r, int slot) { return r * ST_CAP + ((slot + r) & (ST_CAP - 1)); }
 
 __device__ __forceinline__ void wg_sync(int g) { asm volatile("bar.sync %0, 128;" ::"r"(g + 1) : "memory"); }
 
@@ -125,6 +131,8 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   }
   cp_async_commit();
   for (int c = tid; c < kC; c += ST_THREADS) sSizeP[c] = (kcounts[(size_t)h * kC + c] << 12) + 1;
+  float* sMom = reinterpret_cast<float*>(sm + OFF_MOM);
+  for (int i = tid; i < kMomFloats; i += ST_THREADS) sMom[i] = mom[(size_t)h * kMomFloats + i];
   __syncthreads();
   {
     // exclusive prefix sums of the query-cluster sizes
@@ -291,7 +299,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
     // 32-vector and a 32 x 32 matrix, fp32) give both in 1056 multiply-adds per row.  Each column group
     // takes eight rows of the matrix.  The statistics only place the first histogram range.
     {
-      const float* mh = mom + (size_t)blockIdx.y * kMomFloats;
+      const float* mh = sMom;
       float qv[32];
 #pragma unroll
       for (int q4 = 0; q4 < 4; ++q4) {
@@ -310,15 +318,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       float s1 = 0.f, s2 = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float* grow = mh + 32 + (8 * g + i) * 32;
+        const float4* grow = reinterpret_cast<const float4*>(mh + 32 + (8 * g + i) * 32);
         float t0 = 0.f, t1 = 0.f;
 #pragma unroll
-        for (int b2 = 0; b2 < 32; b2 += 2) {
-          t0 = fmaf(__ldg(grow + b2), qv[b2], t0);
-          t1 = fmaf(__ldg(grow + b2 + 1), qv[b2 + 1], t1);
+        for (int b4 = 0; b4 < 8; ++b4) {
+          const float4 mm = grow[b4];      // the same address in every thread of the group: a broadcast
+          t0 = fmaf(mm.x, qv[4 * b4], t0);
+          t1 = fmaf(mm.y, qv[4 * b4 + 1], t1);
+          t0 = fmaf(mm.z, qv[4 * b4 + 2], t0);
+          t1 = fmaf(mm.w, qv[4 * b4 + 3], t1);
         }
         s2 = fmaf(qa[i], t0 + t1, s2);
-        s1 = fmaf(qa[i], __ldg(mh + 8 * g + i), s1);
+        s1 = fmaf(qa[i], mh[8 * g + i], s1);
       }
       sPart[(1 * 4 + g) * 128 + r] = s1;
       sPart[(2 * 4 + g) * 128 + r] = s2;
@@ -481,7 +492,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             sumA += above ? pp[e] : 0;
             if (!above && a >= thrW) {
               const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
-              if (slot < ST_CAP) sCand[r * ST_CAP + slot] = (uint32_t)(cbase + j4 + e);
+              if (slot < ST_CAP) sCand[cand_at(r, slot)] = (uint32_t)(cbase + j4 + e);
             }
             wbits |= above ? (1u << (j4 + e)) : 0u;
           }
@@ -522,7 +533,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
           q[8 * q4 + 6] = bf_lo(w.w); q[8 * q4 + 7] = bf_hi(w.w);
         }
         for (int slot = g; slot < n; slot += 4) {
-          const int c = (int)(sCand[r * ST_CAP + slot] & 0xFFFFu);
+          const int c = (int)(sCand[cand_at(r, slot)] & 0xFFFFu);
           float acc = 0.f;
 #pragma unroll
           for (int q4 = 0; q4 < 4; ++q4) {
@@ -532,20 +543,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             acc = fmaf(q[8 * q4 + 4], bf_lo(w.z), acc); acc = fmaf(q[8 * q4 + 5], bf_hi(w.z), acc);
             acc = fmaf(q[8 * q4 + 6], bf_lo(w.w), acc); acc = fmaf(q[8 * q4 + 7], bf_hi(w.w), acc);
           }
-          sCand[r * ST_CAP + slot] = (uint32_t)c | ((uint32_t)key16_from_score(acc) << 16);
+          sCand[cand_at(r, slot)] = (uint32_t)c | ((uint32_t)key16_from_score(acc) << 16);
         }
       }
     }
     __syncthreads();
 
-    // ---- walk the candidates in exact order; queue what could not be settled -------
+    // ---- settle the candidates in exact order; queue what could not be settled -------
+    // Walking the candidates in (key descending, index ascending) order until the budget is met selects
+    // candidate j iff the tokens above the window plus the sizes of the candidates before j stay below ns.
+    // "Before" is a comparison of the entries with their low 16 bits flipped, so every candidate can be
+    // decided on its own: first one thread per row validates the window, then four threads per row take a
+    // quarter of the candidates each.
     if (g == 0) {
       int st = sRowI[R_STATE * 128 + r];
       const int n = sRowI[R_NCAND * 128 + r];
-      const int orig = sRowI[R_ORIG * 128 + r];
-      uint32_t* myUnion = sUnion + (sRowI[R_SEG * 128 + r] & (ST_MAXSEG - 1)) * 64;
       if (st == RS_COLLECT) {
-        int running = sRowI[R_SIZEA * 128 + r];
+        const int running = sRowI[R_SIZEA * 128 + r];
         // Independent of how the window was found, the result is exact iff the exact threshold key lies
         // inside it: fewer than ns tokens have a key >= y = thrA - e' (every cluster above the window does,
         // plus the candidates counted here), and at least ns have a key >= z = thrW + e'.
@@ -554,46 +568,48 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
           const float e1 = 0.5f * sRowF[R_E2 * 128 + r];
           const uint32_t ky = (uint32_t)key16_from_half(__float2half_ru(sRowF[R_THRA * 128 + r] - e1));
           const uint32_t kz = (uint32_t)key16_from_half(__float2half_ru(sRowF[R_THRW * 128 + r] + e1));
-          int sy = running, sz2 = running;
+          int sy = running, sz2 = running, tot = running;
           for (int s2 = 0; s2 < n; ++s2) {
-            const uint32_t e = sCand[r * ST_CAP + s2];
+            const uint32_t e = sCand[cand_at(r, s2)];
             const int szc = sSizeP[e & 0xFFFFu] >> 12;
             sy += (e >> 16) >= ky ? szc : 0;
             sz2 += (e >> 16) >= kz ? szc : 0;
+            tot += szc;
           }
-          why = sy >= ns ? 5 : (sz2 < ns ? 6 : 0);
+          // 7: the window does not reach the budget, let the exact kernel decide
+          why = sy >= ns ? 5 : (sz2 < ns ? 6 : (tot < ns ? 7 : 0));
         }
-        if (why) {
-          st = RS_QUEUE + why;
-        } else {
-          unsigned long long used = 0ull;
-          int rc = -1;
-          while (running < ns) {
-            int best = -1;
-            uint32_t bkey = 0u, bidx = 0u;
-            for (int s2 = 0; s2 < n; ++s2) {
-              if ((used >> s2) & 1ull) continue;
-              const uint32_t e = sCand[r * ST_CAP + s2];
-              const uint32_t k = e >> 16, c = e & 0xFFFFu;
-              if (best < 0 || k > bkey || (k == bkey && c < bidx)) { best = s2; bkey = k; bidx = c; }
-            }
-            if (best < 0) break;
-            used |= 1ull << best;
-            const int sz = sSizeP[bidx] >> 12;
-            const uint32_t bit = 1u << (bidx & 31);
-            if (!(myUnion[bidx >> 5] & bit)) atomicOr(&myUnion[bidx >> 5], bit);
-            if (running + sz >= ns) rc = running + sz;
-            running += sz;
-          }
-          if (rc < 0) st = RS_QUEUE + 7;  // the window did not reach the budget: let the exact kernel decide
-          else rowcnt[(size_t)h * N + orig] = rc;
-        }
+        st = why ? RS_QUEUE + why : RS_WALK;
+        sRowI[R_STATE * 128 + r] = st;
       }
-      if (st >= RS_QUEUE) {
+      if (st >= RS_QUEUE && st != RS_WALK) {
         int* qh = fixq + (size_t)h * (2 * (size_t)N + 1);
         const int slot = atomicAdd(qh, 1);
-        qh[1 + 2 * slot] = orig;
+        qh[1 + 2 * slot] = sRowI[R_ORIG * 128 + r];
         qh[2 + 2 * slot] = sRowI[R_CLU * 128 + r] | ((st - RS_QUEUE) << 24);      // the reason rides in the top byte
+      }
+    }
+    __syncthreads();
+    if (sRowI[R_STATE * 128 + r] == RS_WALK) {
+      const int n = sRowI[R_NCAND * 128 + r];
+      const int running = sRowI[R_SIZEA * 128 + r];
+      uint32_t* myUnion = sUnion + (sRowI[R_SEG * 128 + r] & (ST_MAXSEG - 1)) * 64;
+      for (int j = g; j < n; j += 4) {
+        const uint32_t ej = sCand[cand_at(r, j)];
+        const uint32_t oj = ej ^ 0xFFFFu;
+        int before = running;
+        for (int i = 0; i < n; ++i) {
+          const uint32_t ei = sCand[cand_at(r, i)];
+          before += (ei ^ 0xFFFFu) > oj ? sSizeP[ei & 0xFFFFu] >> 12 : 0;
+        }
+        if (before < ns) {
+          const uint32_t cj = ej & 0xFFFFu;
+          const uint32_t bit = 1u << (cj & 31);
+          if (!(myUnion[cj >> 5] & bit)) atomicOr(&myUnion[cj >> 5], bit);
+          const int after = before + (sSizeP[cj] >> 12);
+          // exactly one candidate crosses the budget: its running count is the row's token count
+          if (after >= ns) rowcnt[(size_t)h * N + sRowI[R_ORIG * 128 + r]] = after;
+        }
       }
     }
     __syncthreads();
