@@ -385,7 +385,10 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             const int pp[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-              const int b = max(__float2int_rd((hi - __uint_as_float(v[j4 + e])) * inv) + ovf, bmin);
+              // floor by an add rounded toward -inf: 1.5 * 2^23 + t has floor(t) in its low mantissa bits for
+              // |t| < 2^22; beyond that the difference keeps the sign of t and is far outside [0, ST_B)
+              const float t = (hi - __uint_as_float(v[j4 + e])) * inv;
+              const int b = max(__float_as_int(__fadd_rd(t, 12582912.0f)) - 0x4B400000 + ovf, bmin);
               if ((unsigned)b < (unsigned)ST_B) atomicAdd(hist_r + b * 128, pp[e]);
             }
           }
