@@ -483,7 +483,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       for (int k = 0; k < nseg; ++k)
         if (segmask[k] != 0u) one_seg = (one_seg == -1) ? k : -2;
       stream([&](int cbase, const uint32_t(&v)[32]) {
-        uint32_t wbits = 0u;
+        // straight-line over the 32 scores: bit masks of the clusters above the window and of those at or
+        // above its lower end; the (few) candidates are appended afterwards from the difference
+        uint32_t wbits = 0u, ibits = 0u;
 #pragma unroll
         for (int j4 = 0; j4 < 32; j4 += 4) {
           const int4 p4 = *reinterpret_cast<const int4*>(sSizeP + cbase + j4);
@@ -493,12 +495,16 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
             const float a = __uint_as_float(v[j4 + e]);
             const bool above = a > thrA;
             sumA += above ? pp[e] : 0;
-            if (!above && a >= thrW) {
-              const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
-              if (slot < ST_CAP) sCand[cand_at(r, slot)] = (uint32_t)(cbase + j4 + e);
-            }
             wbits |= above ? (1u << (j4 + e)) : 0u;
+            ibits |= a >= thrW ? (1u << (j4 + e)) : 0u;
           }
+        }
+        uint32_t cbits = ibits & ~wbits;
+        while (cbits) {
+          const int j = __ffs(cbits) - 1;
+          cbits &= cbits - 1u;
+          const int slot = atomicAdd(&sRowI[R_NCAND * 128 + r], 1);
+          if (slot < ST_CAP) sCand[cand_at(r, slot)] = (uint32_t)(cbase + j);
         }
         // clusters some row of this warp takes outright -> the bitmap of the rows' segment(s)
         const uint32_t any = __reduce_or_sync(0xffffffffu, wbits);
