@@ -100,6 +100,25 @@ def test_operator_is_deterministic(small_case):
     assert torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))
 
 
+def test_caller_owned_output_tensor(small_case):
+    """step(..., out=t) writes the same bits into t and leaves the previous result alone."""
+    from token2tile_b200 import MaskedStepDeploy
+    c = small_case
+    op = MaskedStepDeploy(c["H"], c["N"], c["CQ"], s_frac=0.05)
+    q, k, v = (c[n].to(DEV) for n in "qkv")
+    state = {n: t.to(DEV) for n, t in c["state"].items()}
+    ref = op.step(q, k, v, state).clone()
+    mine = torch.full_like(ref, 7.0)
+    state = {n: t.to(DEV) for n, t in c["state"].items()}
+    got = op.step(q, k, v, state, out=mine)
+    torch.cuda.synchronize()
+    assert got is mine and torch.equal(mine.view(torch.int16), ref.view(torch.int16))
+    with pytest.raises(ValueError):
+        op.step(q, k, v, state, out=mine.float())
+    with pytest.raises(ValueError):
+        op.step(q, k, v, state, out=mine[:, :-1])
+
+
 def test_init_state_projection_fit(small_case):
     from token2tile_b200 import MaskedStepDeploy
     c = small_case

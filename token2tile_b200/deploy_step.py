@@ -364,12 +364,20 @@ class MaskedStepDeploy:
         return snap, self._struct, False
 
     # -- the attention call ------------------------------------------------------
-    def step(self, q, k, v, state):
+    def step(self, q, k, v, state, out=None):
         """q, k, v: [H, N, 128] bfloat16 contiguous, original row order.  state:
         dict(Uq, Uk, ck, cq); ck / cq are replaced by the centroids that
-        warm-start the next call.  Returns out [H, N, 128] bfloat16, a buffer
-        owned by the operator and overwritten by the next call."""
+        warm-start the next call.  Returns out [H, N, 128] bfloat16: the tensor
+        passed as `out` (same shape, dtype, device, contiguous), else a buffer
+        owned by the operator and overwritten by the next call.  A caller that
+        still reads the previous result while the next call runs (a copy to the
+        host in flight, say) alternates two `out` tensors."""
         self._check_qkv(q, k, v)
+        if out is None:
+            out = self.tile_attn_out
+        elif (out.shape != self.tile_attn_out.shape or out.dtype != BF16 or out.device != self.tile_attn_out.device
+              or not out.is_contiguous()):
+            raise ValueError("out must be a contiguous bfloat16 tensor [H, N, 128] on the operator's device")
         caller = torch.cuda.current_stream(self.dev)
         if caller != self.s_main:
             self.s_main.wait_stream(caller)
@@ -433,7 +441,7 @@ class MaskedStepDeploy:
             self._mark("attn_exact")
             check(L.t2t_tile_attn_merge(
                 ptr(self.QU), ptr(S["cks"]), ptr(self._kmm_sumv), ptr(S["counts"]), ptr(S["unip"]),
-                ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(self.tile_attn_out),
+                ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(out),
                 H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_merge")
             self._mark("residual_merge")
         self.last_rebuilt = snap is None
@@ -442,7 +450,7 @@ class MaskedStepDeploy:
         cur = torch.cuda.current_stream(self.dev)
         cur.wait_stream(self.s_main)
         cur.wait_stream(self.s_side)
-        return self.tile_attn_out
+        return out
 
     # -- diagnostics -------------------------------------------------------------
     def device_status(self) -> int:
