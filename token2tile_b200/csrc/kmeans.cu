@@ -241,17 +241,50 @@ __global__ void __launch_bounds__(CS_WARPS * 32) fixed_mean_kernel(
   const int cnt = counts[(size_t)h * Cn + c];
   const int* srt = perm + (size_t)h * N + cbase[(size_t)h * Cn + c];
   const __nv_bfloat16* Xh = X + (size_t)h * N * kR;
-  long long acc = 0;
-  for (int i = 0; i < cnt; i += CS_UNR) {
-    float v[CS_UNR];
+  // Integer sums do not depend on the order: four lanes read one 64-byte row (16 bytes = 8 dimensions each),
+  // so a load instruction covers eight rows; the eight row slots are added up by shuffles at the end.
+  const int slot = lane >> 2, part = lane & 3;
+  long long acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  constexpr int U = 4;
+  for (int i = 0; i < cnt; i += 8 * U) {
+    uint4 w[U];
 #pragma unroll
-    for (int u = 0; u < CS_UNR; ++u)
-      v[u] = (i + u < cnt) ? bf_to_f(Xh[(size_t)srt[i + u] * kR + lane]) : 0.f;
+    for (int u = 0; u < U; ++u) {
+      const int j = i + 8 * u + slot;
+      w[u] = j < cnt ? *reinterpret_cast<const uint4*>(Xh + (size_t)srt[j] * kR + part * 8) : make_uint4(0u, 0u, 0u, 0u);
+    }
 #pragma unroll
-    for (int u = 0; u < CS_UNR; ++u) acc += (long long)__float2int_rn(v[u] * 32768.0f);
+    for (int u = 0; u < U; ++u) {
+      const uint32_t ws[4] = {w[u].x, w[u].y, w[u].z, w[u].w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += (long long)__float2int_rn(bf_lo(ws[e]) * 32768.0f);
+        acc[2 * e + 1] += (long long)__float2int_rn(bf_hi(ws[e]) * 32768.0f);
+      }
+    }
   }
-  const size_t o = ((size_t)h * Cn + c) * kR + lane;
-  newc[o] = cnt ? __float2bfloat16_rn((float)acc / (32768.0f * (float)cnt)) : old[o];
+#pragma unroll
+  for (int d = 4; d < 32; d <<= 1)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], d);
+  if (slot == 0) {
+    // lane `part` holds dimensions 8 part .. 8 part + 7
+    const size_t o = ((size_t)h * Cn + c) * kR + part * 8;
+    uint32_t outw[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      __nv_bfloat16 lo, hi;
+      if (cnt) {
+        lo = __float2bfloat16_rn((float)acc[2 * e] / (32768.0f * (float)cnt));
+        hi = __float2bfloat16_rn((float)acc[2 * e + 1] / (32768.0f * (float)cnt));
+      } else {
+        lo = old[o + 2 * e];
+        hi = old[o + 2 * e + 1];
+      }
+      outw[e] = (uint32_t)__bfloat16_as_ushort(lo) | ((uint32_t)__bfloat16_as_ushort(hi) << 16);
+    }
+    *reinterpret_cast<uint4*>(newc + o) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+  }
 }
 
 // Key side: fp32 sums accumulated one row at a time in grouped order, then the
