@@ -916,12 +916,15 @@ static_assert(3 * TL_SMEM > 227 * 1024, "at most two CTAs may share an SM");
 //   softmax rows  wait sReady[b]; p = exp2(S_b - m) masked by the row's union, packed to bf16 into S_b;
 //                 arrive on pReady[b]
 //   MMA lane      wait pReady[b]; T += P_b sumv_i; S_b = QU cks_{i+2}^T; commit on sReady[b]
-// so the tensor work of one region runs under the softmax of the other.  The softmax threads also feed
-// the rings: at the start of step i they issue the cp.async copies of sumv_{i+1} and cks_{i+3} into the
-// stages that sReady[b] has just declared free, and before arriving on pReady[b] they wait for the copies
-// of the previous step (sumv_i, cks_{i+2}), which the MMA lane is about to read.
+// so the tensor work of one region runs under the softmax of the other.  Two rings feed the products.  The
+// softmax threads issue the cp.async copies of cks_{i+3} at the start of step i, into the stage that
+// sReady[b] has just declared free, and before arriving on pReady[b] they wait for the copy issued one step
+// earlier (cks_{i+2}), which the MMA lane is about to read.  The MMA lane itself fetches sumv_{i+1} with two
+// TMA tile loads once pReady[b] of step i shows that every row has seen the commit behind the product of
+// step i - 2, and waits for sumv_i on the stage's byte-counting barrier before T += P_b sumv_i.
 __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
-    const __grid_constant__ CUtensorMap mapSumv, const __nv_bfloat16* __restrict__ attn_out, const float* __restrict__ attn_lse,
+    const __grid_constant__ CUtensorMap mapSumv, const __nv_bfloat16* __restrict__ attn_out,
+    const float* __restrict__ attn_lse,
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
     const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
     const int* __restrict__ qlab, const int* __restrict__ qperm, const float* __restrict__ lam_s,
