@@ -771,13 +771,19 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       // before it waits for a group's P, and then issues P V and the next Q K^T back to back.
       if (lane == 0) {
         bool ok = true;
+        // descriptor low words of the tiles (the K steps add constants to them), one high word for all
+        constexpr uint32_t dhi = sdesc_hi(1024);
+        const uint32_t qlo[2] = {sdesc_lo(base, 16), sdesc_lo(base + AT_TILE, 16)};
+        const uint32_t klo[2] = {sdesc_lo(base + A2_OFF_SLOT, 16), sdesc_lo(base + A2_OFF_SLOT + A2_SLOT, 16)};
+        const uint32_t vlo[2] = {sdesc_lo(base + A2_OFF_SLOT + AT_TILE, KT * 128),
+                                 sdesc_lo(base + A2_OFF_SLOT + A2_SLOT + AT_TILE, KT * 128)};
         auto mma_qk = [&](int g, uint32_t slot) {      // S_g = Q_g K^T for the K tile in ring slot `slot`
-          const uint32_t sQ = base + g * AT_TILE, sK = base + A2_OFF_SLOT + slot * A2_SLOT;
+          const uint32_t a0 = qlo[g], b0 = slot ? klo[1] : klo[0];
 #pragma unroll
           for (int s = 0; s < 8; ++s) {
-            const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
-            const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
-            umma_ss(tmem + g * 256, ad, bd, idescQK, s > 0 ? 1u : 0u);
+            constexpr uint32_t blk = (QT * 128) >> 4;      // second 64-column block of a tile
+            const uint32_t off = (s >> 2) * blk + (s & 3) * 2;
+            umma_ss_lo(tmem + g * 256, a0 + off, b0 + off, dhi, idescQK, s > 0 ? 1u : 0u);
           }
           umma_commit(bars + B_S + g);
           if (g == 1) umma_commit(bars + B_FREEK + slot);      // covers group 0's MMAs too: same issuer, in order
@@ -793,7 +799,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
         for (int t = 0; t < ntiles && ok; ++t) {
           const uint32_t tg = g0 + t, slot = tg & 1u;
           const bool more = t + 1 < ntiles;
-          const uint32_t sV = base + A2_OFF_SLOT + slot * A2_SLOT + AT_TILE;
+          const uint32_t v0 = slot ? vlo[1] : vlo[0];
           if (!mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) break;
           if (more && !mbar_wait(bars + B_FULLK + (slot ^ 1u), ((tg + 1) >> 1) & 1u, abort_flag)) break;
 #pragma unroll
@@ -803,10 +809,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
             tc_fence_after();
             const uint32_t tS = tmem + g * 256, tO = tS + 128;
 #pragma unroll
-            for (int s8 = 0; s8 < 8; ++s8) {
-              const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
-              umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
-            }
+            for (int s8 = 0; s8 < 8; ++s8)
+              umma_ts_lo(tO, tS + s8 * 8, v0 + s8 * (2048 >> 4), dhi, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
             umma_commit(bars + B_O + g);
             if (g == 1) umma_commit(bars + B_FREEV + slot);
             if (more) mma_qk(g, slot ^ 1u);
