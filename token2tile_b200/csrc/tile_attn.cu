@@ -655,6 +655,9 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = (warp >> 2) & 1, gt = tid & 127, gw = warp & 3;   // softmax warps: group, thread, warp in group
 
+  // the kernel launched behind this one (tasks of at most QT rows) does not depend on it: let it be scheduled
+  // as soon as SMs free up
+  asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
   if (warp == 0) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
@@ -1258,8 +1261,23 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   // tasks above 128 rows first (one CTA per SM, two row tiles per K/V stream), then the others
   attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out,
                                                  attn_lse, plan, H, N, CQ, d_status);
-  attn_kernel<<<2 * sms, 128, AT_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
-                                             plan, H, N, CQ, d_status);
+  // The two kernels take disjoint tasks (own cursors, own output rows), so the second may start while the
+  // first drains: it is launched with programmatic stream serialization and the first kernel releases its
+  // dependents at once.  Their CTAs cannot share an SM (shared memory), so the second kernel's CTAs move in
+  // as the first kernel's CTAs run out of tasks and exit.  Later work in the stream waits for both as usual.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * sms);
+  cfg.blockDim = dim3(128);
+  cfg.dynamicSmemBytes = AT_SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, attn_kernel, mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
+                         plan, H, N, CQ, d_status) != cudaSuccess)
+    return T2T_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
 
