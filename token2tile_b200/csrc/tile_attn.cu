@@ -543,6 +543,11 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 256);
+  // This kernel may have started while the kernel launched before it (the tasks above QT rows) was still
+  // running.  No CTA leaves before that grid has completed and its results are visible, so that this grid's
+  // completion, which later work in the stream waits for, implies the other's.  (Without a programmatic
+  // launch the instruction returns at once.)
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------
