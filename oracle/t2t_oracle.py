@@ -53,19 +53,63 @@ def round16(x: torch.Tensor, dt: torch.dtype) -> torch.Tensor:
     return x.to(dt).to(F32)
 
 
-def chain_dot(x: torch.Tensor, c: torch.Tensor, init: torch.Tensor | None = None) -> torch.Tensor:
-    """fp32 chain  acc <- acc + x[:, k] * c[:, k]  for k in order.
+_CHAIN_LIB = False          # False: not looked for yet; None: unavailable
 
-    x [n, r] fp32 (16-bit values), c [m, r] fp32 (16-bit values),
-    init [m] fp32 or None (0).  Returns [n, m] fp32."""
+
+def _chain_lib():
+    """The C twin of the chain (oracle/chain_dot.c), built on first use when a C
+    compiler is present; None otherwise."""
+    global _CHAIN_LIB
+    if _CHAIN_LIB is False:
+        _CHAIN_LIB = None
+        try:
+            import ctypes
+            import importlib.util
+            from pathlib import Path
+            spec = importlib.util.spec_from_file_location("_t2t_oracle_build_c", Path(__file__).with_name("build_c.py"))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            path = mod.build()
+            if path is not None:
+                lib = ctypes.CDLL(str(path))
+                lib.t2t_chain_dot.restype = ctypes.c_int
+                lib.t2t_chain_dot.argtypes = [ctypes.c_void_p] * 4 + [ctypes.c_long, ctypes.c_long, ctypes.c_int]
+                _CHAIN_LIB = lib
+        except Exception:       # no compiler, read-only tree, ...: the PyTorch loop below is the definition anyway
+            _CHAIN_LIB = None
+    return _CHAIN_LIB
+
+
+def chain_dot_loop(x: torch.Tensor, c: torch.Tensor, init: torch.Tensor | None = None) -> torch.Tensor:
+    """The definition of the chain, as a PyTorch loop over k."""
     n, r = x.shape
     m = c.shape[0]
-    if FAST_DOT:
-        return x @ c.T if init is None else torch.addmm(init[None, :].expand(n, m), x, c.T)
     acc = torch.zeros(n, m, dtype=F32) if init is None else init[None, :].expand(n, m).clone()
     for k in range(r):
         acc += x[:, k:k + 1] * c[None, :, k]
     return acc
+
+
+def chain_dot(x: torch.Tensor, c: torch.Tensor, init: torch.Tensor | None = None) -> torch.Tensor:
+    """fp32 chain  acc <- acc + x[:, k] * c[:, k]  for k in order.
+
+    x [n, r] fp32 (16-bit values), c [m, r] fp32 (16-bit values),
+    init [m] fp32 or None (0).  Returns [n, m] fp32.  Uses the C twin of the
+    loop when it could be built (same bits, all host threads)."""
+    n, r = x.shape
+    m = c.shape[0]
+    if FAST_DOT:
+        return x @ c.T if init is None else torch.addmm(init[None, :].expand(n, m), x, c.T)
+    lib = _chain_lib()
+    if lib is None or x.device.type != "cpu":
+        return chain_dot_loop(x, c, init)
+    xc, cc = x.to(F32).contiguous(), c.to(F32).contiguous()
+    ic = None if init is None else init.to(F32).contiguous()
+    out = torch.empty(n, m, dtype=F32)
+    rc = lib.t2t_chain_dot(xc.data_ptr(), cc.data_ptr(), 0 if ic is None else ic.data_ptr(), out.data_ptr(), n, m, r)
+    if rc != 0:
+        raise RuntimeError(f"t2t_chain_dot failed: {rc}")
+    return out
 
 
 def centroid_norms(c: torch.Tensor) -> torch.Tensor:
@@ -263,17 +307,8 @@ def select_rows(keys: torch.Tensor, sizes: torch.Tensor, ns: int):
     is < ns (select_union/src/kernel.cu:288-392).  rowcnt is the inclusive
     total at the crossing.  keys [n, C] int16, sizes [C] int32.
     Returns (sel [n, C] bool, rowcnt [n] int32)."""
-    n, C = keys.shape
     order = torch.sort(-keys.to(torch.int32), dim=1, stable=True).indices
-    sz = sizes.to(torch.int64)[order]
-    incl = torch.cumsum(sz, dim=1)
-    excl = incl - sz
-    sel_sorted = excl < ns
-    sel = torch.zeros(n, C, dtype=torch.bool).scatter_(1, order, sel_sorted)
-    cross = (incl >= ns).to(torch.uint8).argmax(dim=1)          # first position reaching ns
-    reached = incl[:, -1] >= ns
-    rowcnt = torch.where(reached, incl.gather(1, cross[:, None])[:, 0], incl[:, -1])
-    return sel, rowcnt.to(torch.int32)
+    return select_rows_sorted(order, sizes, ns)
 
 
 def pack_bits(sel: torch.Tensor) -> torch.Tensor:
@@ -290,6 +325,48 @@ def unpack_bits(words: torch.Tensor, C: int) -> torch.Tensor:
     return ((w[..., None] >> torch.arange(32, dtype=torch.int64)) & 1).bool().reshape(*words.shape[:-1], C)
 
 
+def select_rows_sorted(order: torch.Tensor, sizes: torch.Tensor, ns: int):
+    """select_rows for a precomputed order (clusters by key descending, index
+    ascending): the selection rule only needs the sizes along that order."""
+    n, C = order.shape
+    sz = sizes.to(torch.int64)[order]
+    incl = torch.cumsum(sz, dim=1)
+    excl = incl - sz
+    sel = torch.zeros(n, C, dtype=torch.bool).scatter_(1, order, excl < ns)
+    cross = (incl >= ns).to(torch.uint8).argmax(dim=1)          # first position reaching ns
+    reached = incl[:, -1] >= ns
+    rowcnt = torch.where(reached, incl.gather(1, cross[:, None])[:, 0], incl[:, -1])
+    return sel, rowcnt.to(torch.int32)
+
+
+def select_union_budgets(QU16, cks16, kcounts, qlab, CQ: int, ns_list, pin_tail: int = 0,
+                         row_chunk: int = 2048, gl16=None):
+    """select_union for several budgets at once: the keys and their order do
+    not depend on the budget, so they are computed once per block of rows.
+    Returns one (unip, rowcnt) pair per entry of ns_list."""
+    H, N = qlab.shape
+    C = kcounts.shape[1]
+    hits = [torch.zeros(H, CQ, C, dtype=torch.int32) for _ in ns_list]
+    rowcnt = [torch.empty(H, N, dtype=torch.int32) for _ in ns_list]
+    for h in range(H):
+        lab = qlab[h].to(torch.int64)
+        for s in range(0, N, row_chunk):
+            keys = (score_keys(QU16[h, s:s + row_chunk], cks16[h]) if gl16 is None
+                    else keys_from_fp16(gl16[h, s:s + row_chunk]))
+            order = torch.sort(-keys.to(torch.int32), dim=1, stable=True).indices
+            for b, ns in enumerate(ns_list):
+                sel, rc = select_rows_sorted(order, kcounts[h], ns)
+                rowcnt[b][h, s:s + row_chunk] = rc
+                hits[b][h].index_add_(0, lab[s:s + row_chunk], sel.to(torch.int32))
+    out = []
+    for b in range(len(ns_list)):
+        union = hits[b] > 0
+        if pin_tail > 0:
+            union[:, :, C - 1] = True
+        out.append((pack_bits(union), rowcnt[b]))
+    return out
+
+
 def select_union(QU16, cks16, kcounts, qlab, CQ: int, ns: int, pin_tail: int = 0,
                  row_chunk: int = 2048, gl16=None):
     """Union bitmap unip [H, CQ, C/32] int32 and rowcnt [H, N] int32.
@@ -297,22 +374,7 @@ def select_union(QU16, cks16, kcounts, qlab, CQ: int, ns: int, pin_tail: int = 0
     sets cluster C-1 everywhere (deploy_step.py:444-448).  With gl16 (an fp16
     score matrix [H, N, C], the reference's `gl`) the scores are taken from it
     instead of being recomputed."""
-    H, N = qlab.shape
-    C = kcounts.shape[1]
-    hits = torch.zeros(H, CQ, C, dtype=torch.int32)
-    rowcnt = torch.empty(H, N, dtype=torch.int32)
-    for h in range(H):
-        lab = qlab[h].to(torch.int64)
-        for s in range(0, N, row_chunk):
-            keys = (score_keys(QU16[h, s:s + row_chunk], cks16[h]) if gl16 is None
-                    else keys_from_fp16(gl16[h, s:s + row_chunk]))
-            sel, rc = select_rows(keys, kcounts[h], ns)
-            rowcnt[h, s:s + row_chunk] = rc
-            hits[h].index_add_(0, lab[s:s + row_chunk], sel.to(torch.int32))
-    union = hits > 0
-    if pin_tail > 0:
-        union[:, :, C - 1] = True
-    return pack_bits(union), rowcnt
+    return select_union_budgets(QU16, cks16, kcounts, qlab, CQ, [ns], pin_tail, row_chunk, gl16)[0]
 
 
 def kv_lengths(unip, qcounts, kcounts) -> torch.Tensor:
