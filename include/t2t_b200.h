@@ -46,6 +46,19 @@ int t2t_version(void);
 int t2t_project(const void* x, const void* U, void* out, int H, int N, int* d_status,
                 cudaStream_t stream);
 
+/* Projection fit: fp32 Uq, Uk [H,128,32] minimising ||Q K^T - (Q Uq)(K Uk)^T||_F
+ * for q, k bf16 [H,N,128].  Second moments on the tensor cores (fp32 slabs of
+ * 8192 rows, summed in fp64 in slab order), symmetric roots and singular
+ * triplets by an fp64 Jacobi kernel (one CTA per matrix, eigenvalues clamped
+ * at 1e-8), all batched over heads on `stream` without a host round trip.
+ * d_bad: int [2 H], set to 1 for a head whose q (first H) or k (last H) holds a
+ * non-finite value; that head's Uq, Uk are left untouched.  ws:
+ * t2t_lowrank_fit_ws_bytes(H, N).  Replaces online_u, deploy_step.py:122-149
+ * (and its batched forms, integrations/sglang/backend/t2t_attn.py:181-239). */
+size_t t2t_lowrank_fit_ws_bytes(int H, int N);
+int t2t_lowrank_fit(const void* q, const void* k, float* Uq, float* Uk, int H, int N, void* ws,
+                    size_t ws_bytes, int* d_bad, int* d_status, cudaStream_t stream);
+
 /* labels[h,i] = argmin_c(||c||^2 - 2 x_i.c), ties to the lowest c; rows >=
  * pin_begin get pin_label when pin_begin >= 0.  x bf16 [H,N,32], cen bf16
  * [H,Cn,32], labels int32 [H,N].  The distance is DEFINED as the fp32

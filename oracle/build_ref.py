@@ -9,6 +9,7 @@ The output is a checker used by tests/test_gpu_ref_pin.py to pin the CPU oracle
 against the reference's real kernels.  The reference's tile_attn sources are
 not built: they use wgmma, which does not exist on sm_100a.
 """
+import os
 import subprocess
 import sys
 from pathlib import Path
@@ -18,7 +19,8 @@ OUT = HERE / "_ref"
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    # the reference checkout: argument, else T2T_REFERENCE_DIR, else a "reference" directory beside this repository
+    ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("T2T_REFERENCE_DIR") or HERE.parent.parent / "reference")
     kern = ref / "token2tile" / "operator" / "kernels"
     kmm, sel = kern / "kmeans_maintain" / "src", kern / "select_union" / "src"
     if not (kmm / "kernels.cu").exists():

@@ -9,6 +9,7 @@ The fixture stores the seeds, not the inputs: the test regenerates q and k with
 the same generator calls.
 """
 import importlib.util
+import os
 import sys
 from pathlib import Path
 
@@ -28,7 +29,9 @@ def make_inputs(case):
 
 
 def main():
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference") / "token2tile" / "operator"
+    here = Path(__file__).resolve()
+    root = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("T2T_REFERENCE_DIR") or here.parents[3] / "reference")
+    ref = root / "token2tile" / "operator"
     sys.path.insert(0, str(ref))
     spec = importlib.util.spec_from_file_location("ref_deploy_step", ref / "deploy_step.py")
     mod = importlib.util.module_from_spec(spec)

@@ -179,3 +179,18 @@ def test_reuse_schedule_follows_the_reference_rule():
             trace.append(snap is None)
     assert trace[:10] == [True, False, False, False, False, False, False, False, True, False]
     assert op._pick_snapshot() is None      # an unannotated call always rebuilds
+
+
+def test_c_twin_of_the_ordered_chain_gives_the_same_bits():
+    """oracle/chain_dot.c against the PyTorch loop that defines the chain."""
+    if O._chain_lib() is None:
+        pytest.skip("no C compiler: the oracle runs the PyTorch loop")
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(777, 32, generator=g).to(torch.bfloat16).float()
+    c = (torch.randn(301, 32, generator=g) * 3).to(torch.bfloat16).float()
+    init = torch.randn(301, generator=g)
+    assert torch.equal(O.chain_dot(x, c, init), O.chain_dot_loop(x, c, init))
+    assert torch.equal(O.chain_dot(x, c), O.chain_dot_loop(x, c))
+    # arbitrary fp32 inputs too: products and sums are rounded separately in both
+    xf, cf = torch.randn(50, 32, generator=g), torch.randn(40, 32, generator=g)
+    assert torch.equal(O.chain_dot(xf, cf), O.chain_dot_loop(xf, cf))

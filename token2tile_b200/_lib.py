@@ -20,6 +20,8 @@ _P, _I, _S, _F = C.c_void_p, C.c_int, C.c_size_t, C.c_float
 SIGNATURES = {
     "t2t_version": (_I, []),
     "t2t_project": (_I, [_P, _P, _P, _I, _I, _P, _P]),
+    "t2t_lowrank_fit_ws_bytes": (_S, [_I, _I]),
+    "t2t_lowrank_fit": (_I, [_P, _P, _P, _P, _I, _I, _P, _S, _P, _P, _P]),
     "t2t_assign_ws_bytes": (_S, [_I, _I]),
     "t2t_assign": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P, _S, _P, _P]),
     "t2t_assign_exact": (_I, [_P, _P, _P, _I, _I, _I, _I, _I, _P]),

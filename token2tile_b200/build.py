@@ -17,7 +17,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 INCLUDE = PKG.parent / "include"
 LIB = PKG / "libt2t_b200.so"
-SOURCES = ["project.cu", "kmeans.cu", "assign_tc.cu", "select.cu", "select_tc.cu", "tile_attn.cu", "tma_rows.cu"]
+SOURCES = ["project.cu", "lowrank_fit.cu", "kmeans.cu", "assign_tc.cu", "select.cu", "select_tc.cu", "tile_attn.cu", "tma_rows.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

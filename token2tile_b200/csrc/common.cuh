@@ -138,6 +138,16 @@ __device__ __forceinline__ void tma_load_tile(uint32_t dst, const void* map, int
       : "memory");
 }
 
+// The same for a 3D tensor (columns, rows, slabs): a (box columns) x (box rows) x 1 tile of slab `slab`.
+// Rows past the tensor's row extent arrive as zeros.
+__device__ __forceinline__ void tma_load_tile3(uint32_t dst, const void* map, int col, int row, int slab, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3, %4}], [%5];\n" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(col), "r"(row), "r"(slab), "r"(smem_u32(bar))
+      : "memory");
+}
+
 // ---- tcgen05 / TMEM ---------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");

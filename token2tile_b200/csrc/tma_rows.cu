@@ -40,6 +40,18 @@ bool make_row_tile_map(void* map_out, const void* base, uint64_t rows, uint32_t 
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+bool make_head_tile_map(void* map_out, const void* base, uint64_t rows_per_head, uint64_t heads, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn || (reinterpret_cast<uintptr_t>(base) & 15u) || box_rows == 0 || box_rows > 256) return false;
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)rows_per_head, (cuuint64_t)heads};
+  const cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)kD * 2 * rows_per_head};
+  const cuuint32_t box[3] = {64, box_rows, 1};
+  const cuuint32_t elem[3] = {1, 1, 1};
+  return fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),
+            dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 bool make_row_gather_map(void* map_out, const void* base, uint64_t rows) {
   return make_row_tile_map(map_out, base, rows, 1);
 }

@@ -15,8 +15,8 @@ shape [H, N, 128] (bfloat16):
   4. attention    exact attention of every query cluster over its
                   union + centroid residual, one softmax            t2t_tile_attn
 
-PyTorch supplies device memory, streams and the two tiny factorisations of the
-projection fit; every stage above is a hand-written CUDA kernel.  There is no
+PyTorch supplies device memory and streams; every stage above, and the
+projection fit of `init_state`, is a hand-written CUDA kernel.  There is no
 CPU path: the module refuses to load without the compiled library.
 """
 from __future__ import annotations
@@ -41,53 +41,63 @@ BF16 = torch.bfloat16
 # low-rank space
 # ---------------------------------------------------------------------------
 
-def _eigh_robust(M):
-    """Symmetric eigendecomposition with the reference's fall-back to the CPU
-    when the device solver does not converge (deploy_step.py:104-111)."""
-    try:
-        return torch.linalg.eigh(M)
-    except torch._C._LinAlgError:
-        e, V = torch.linalg.eigh(M.cpu())
-        return e.to(M.device), V.to(M.device)
+def lowrank_fit(q, k, r=32, *, check_finite=True):
+    """Runs the projection-fit kernels (t2t_lowrank_fit) on q, k [H, N, 128] and
+    returns fp32 Uq, Uk [H, 128, r].
 
+    The second moments Mq = Q^T Q / N, Mk = K^T K / N come from the tensor cores
+    (bfloat16 inputs, fp32 slabs summed in fp64 in a fixed order); their
+    symmetric roots and the singular triplets of Mq^(1/2) Mk^(1/2) come from an
+    fp64 Jacobi kernel, one CTA per matrix, batched over heads.  Inputs of
+    another dtype are rounded to bfloat16 first: the operator's own tensors are
+    bfloat16, so nothing is lost on its path.
 
-def _svd_robust(M):
-    try:
-        return torch.linalg.svd(M)
-    except torch._C._LinAlgError:
-        U, S, Vh = torch.linalg.svd(M.cpu())
-        return U.to(M.device), S.to(M.device), Vh.to(M.device)
+    check_finite=True reads one flag per head back (a host synchronisation) and
+    raises RuntimeError for non-finite inputs, like the reference
+    (deploy_step.py:127-132); check_finite=False returns without synchronising
+    and leaves the projections of such a head at zero."""
+    if r != 32:
+        raise ValueError("the kernels require r=32")
+    if q.dim() != 3 or q.shape[2] != 128 or k.shape != q.shape or not q.is_cuda or k.device != q.device:
+        raise ValueError(f"lowrank_fit: expected CUDA tensors [H, N, 128] of one shape, got {tuple(q.shape)} "
+                         f"and {tuple(k.shape)}")
+    lib = _lib.load()
+    qb = q if q.dtype == BF16 else q.to(BF16)
+    kb = k if k.dtype == BF16 else k.to(BF16)
+    qb, kb = qb.contiguous(), kb.contiguous()
+    H, N, D = qb.shape
+    dev = qb.device
+    Uq = torch.zeros(H, D, r, device=dev, dtype=torch.float32)
+    Uk = torch.zeros(H, D, r, device=dev, dtype=torch.float32)
+    flags = torch.zeros(2 * H + 1, device=dev, dtype=torch.int32)       # [2 H] non-finite, [1] wait status
+    ws = torch.empty(int(lib.t2t_lowrank_fit_ws_bytes(H, N)), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.t2t_lowrank_fit(ptr(qb), ptr(kb), ptr(Uq), ptr(Uk), H, N, ptr(ws), ws.numel(), ptr(flags),
+                                  ptr(flags) + 8 * H, _stream_ptr(torch.cuda.current_stream(dev))), "t2t_lowrank_fit")
+    if check_finite:
+        f = flags.cpu()
+        if int(f[2 * H]) != 0:
+            raise RuntimeError("lowrank_fit: a bounded device wait timed out")
+        for name, part in (("q", f[:H]), ("k", f[H:2 * H])):
+            if bool(part.any()):
+                raise RuntimeError(f"online_u: non-finite {name} input in heads {part.nonzero()[:, 0].tolist()}, "
+                                   f"shape {tuple(q.shape)}")
+    return Uq, Uk
 
 
 def online_u(qf, kf, r=32):
-    """Matched rank-r projections Uq, Uk [H, D, r] (fp32) minimising
-    ||Q K^T - (Q Uq)(K Uk)^T||_F (deploy_step.py:122-149): with second moments
-    Mq, Mk and the SVD Mq^(1/2) Mk^(1/2) = U S V^T, Uq = Mq^(-1/2) U_r S_r^(1/2)
-    and Uk = Mk^(-1/2) V_r S_r^(1/2).  All factorisations run in fp64."""
-    for name, t in (("q", qf), ("k", kf)):
-        bad = ~torch.isfinite(t)
-        if bool(bad.any()):
-            raise RuntimeError(
-                f"online_u: non-finite {name} input; per-head counts "
-                f"{bad.sum(dim=(1, 2)).tolist()}, shape {tuple(t.shape)}")
-    Uqs, Uks = [], []
-    for h in range(qf.shape[0]):
-        q, k = qf[h].double(), kf[h].double()
-        Mq = (q.T @ q) / q.shape[0]
-        Mk = (k.T @ k) / k.shape[0]
-        eq, Vq = _eigh_robust(Mq)
-        ek, Vk = _eigh_robust(Mk)
-        eq = eq.clamp_min(1e-8)
-        ek = ek.clamp_min(1e-8)
-        Rq = Vq @ torch.diag(eq.sqrt()) @ Vq.T
-        Rk = Vk @ torch.diag(ek.sqrt()) @ Vk.T
-        Rqi = Vq @ torch.diag(eq.rsqrt()) @ Vq.T
-        Rki = Vk @ torch.diag(ek.rsqrt()) @ Vk.T
-        U, S, Vh = _svd_robust(Rq.T @ Rk)
-        sr = S[:r].sqrt()
-        Uqs.append((Rqi.T @ U[:, :r] * sr).float())
-        Uks.append((Rki @ Vh[:r].T * sr).float())
-    return torch.stack(Uqs), torch.stack(Uks)
+    """Matched rank-r projections Uq, Uk [H, 128, r] (fp32) that minimise
+    ||Q K^T - (Q Uq)(K Uk)^T||_F; same contract as the reference's function of
+    this name (deploy_step.py:122-149).  With the second moments Mq, Mk and the
+    singular value decomposition Mq^(1/2) Mk^(1/2) = U S V^T (eigenvalues of
+    the moments clamped at 1e-8),
+
+        Uq = Mq^(-1/2) U_r S_r^(1/2),    Uk = Mk^(-1/2) V_r S_r^(1/2).
+
+    The columns are defined up to a common sign (and a rotation inside equal
+    singular values): compare Uq Uk^T, not the factors.  Runs on the GPU only
+    (see `lowrank_fit`); raises RuntimeError for non-finite inputs."""
+    return lowrank_fit(qf, kf, r, check_finite=True)
 
 
 def _stream_ptr(stream) -> int:
@@ -308,7 +318,7 @@ class MaskedStepDeploy:
         and the deterministic fixed-point centroid update."""
         self._check_qkv(q, k)
         N, r = self.N, self.r
-        Uq, Uk = online_u(q.float(), k.float(), r)
+        Uq, Uk = online_u(q, k, r)
         Uq = Uq.to(BF16).contiguous()
         Uk = Uk.to(BF16).contiguous()
         st = _stream_ptr(torch.cuda.current_stream(self.dev))

@@ -559,46 +559,16 @@ def _set_budget(deploy, ns_tensor, device) -> None:
 # ---------------------------------------------------------------------------
 # fast state initialisation
 # ---------------------------------------------------------------------------
-def _eigh_ridge(matrix):
-    """Batched symmetric eigendecomposition; retries with a growing ridge, then
-    on the CPU (t2t_attn.py:160-170)."""
-    scale = matrix.diagonal(dim1=-2, dim2=-1).mean(dim=-1).clamp_min(1e-12)[:, None, None]
-    eye = torch.eye(matrix.shape[-1], dtype=matrix.dtype, device=matrix.device)
-    for eps in (0.0, 1e-10, 1e-8, 1e-6):
-        try:
-            return torch.linalg.eigh(matrix + eps * scale * eye)
-        except torch._C._LinAlgError:
-            continue
-    values, vectors = torch.linalg.eigh(matrix.cpu())
-    return values.to(matrix.device), vectors.to(matrix.device)
-
-
-def _sqrt_pair(gram):
-    """Symmetric square root and inverse square root of a batch of second-moment
-    matrices, eigenvalues clamped at 1e-8."""
-    e, v = _eigh_ridge(gram)
-    e = e.clamp_min(1e-8)
-    vt = v.transpose(1, 2)
-    return v @ (e.sqrt().unsqueeze(-1) * vt), v @ (e.rsqrt().unsqueeze(-1) * vt)
-
-
 def fast_online_u(qf, kf, r: int = 32):
-    """The projection fit of `online_u`, batched over heads, with the N-long
-    second-moment products in fp32 and only the 128x128 factorisations in fp64;
-    the top-r singular triplets come from an eigendecomposition of M^T M
-    (t2t_attn.py:211-239).  No host-synchronising finiteness check."""
-    n = qf.shape[1]
-    rq, rqi = _sqrt_pair((torch.bmm(qf.transpose(1, 2), qf) / n).double())
-    rk, rki = _sqrt_pair((torch.bmm(kf.transpose(1, 2), kf) / n).double())
-    m = rq.transpose(1, 2) @ rk
-    w, v = _eigh_ridge(m.transpose(1, 2) @ m)
-    v_r = v[:, :, -r:].flip(-1)
-    s_r = w[:, -r:].flip(-1).clamp_min(1e-30).sqrt()
-    u_r = (m @ v_r) / s_r.unsqueeze(1)
-    root = s_r.sqrt().unsqueeze(1)
-    uq = (rqi.transpose(1, 2) @ u_r) * root
-    uk = (rki @ v_r) * root
-    return uq.float().contiguous(), uk.float().contiguous()
+    """The projection fit without the host-synchronising finiteness check
+    (the reference's `_fast_online_u`, t2t_attn.py:211-239, moves the long
+    products to fp32 tensor-core GEMMs and keeps only the 128x128
+    factorisations in fp64).  Here `online_u` already works that way: both
+    names run the same kernels (tensor-core second moments, fp64 Jacobi
+    factorisations, batched over heads); this one returns as soon as the
+    kernels are queued."""
+    from .deploy_step import lowrank_fit
+    return lowrank_fit(qf, kf, r, check_finite=False)
 
 
 def make_fast_init_state(deploy, module=None):
@@ -609,7 +579,7 @@ def make_fast_init_state(deploy, module=None):
 
     def init_state(q, k, *, warm_iters=4, seed=0):
         N, r = deploy.N, deploy.r
-        Uq, Uk = fast_online_u(q.float(), k.float(), r)
+        Uq, Uk = fast_online_u(q, k, r)
         Uq = Uq.to(KERNEL_DTYPE).contiguous()
         Uk = Uk.to(KERNEL_DTYPE).contiguous()
         st = torch.cuda.current_stream(deploy.dev).cuda_stream
