@@ -28,7 +28,7 @@ def test_workspace_sizes_are_pure_host_functions(lib):
     assert lib.t2t_vstats_gather_ws_bytes(40, 2048) >= 40 * 2048 * 128 * 4
     assert lib.t2t_tile_attn_ws_bytes(2, 4096) >= 2 * 4096 * (256 + 4)
     ints = lib.t2t_tile_attn_plan_ints(40, 75600, 512)
-    assert ints >= 40 * 2049 + 4 * 40 * (512 + 591) + 40 * 512
+    assert ints >= 40 * 2049 + 4 * 40 * (512 + 75600 // 256) + 40 * 512
     assert lib.t2t_centroid_update_ws_bytes(2, 4096, 2048) > 0
 
 

@@ -23,6 +23,8 @@
 // a status word and leaves.
 #include <cuda.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "internal.h"
 #include "t2t_b200.h"
@@ -37,20 +39,25 @@ constexpr int PLAN_SORT_MAX = 2048;
 constexpr int PLAN_HDR = 8;      // counters: [0] tasks, [1] cursor of the one-tile kernel, [2..3] executed pairs (lo, hi),
                                  //           [4] cursor of the two-tile kernel
 
-// the counters start on a 16-byte boundary (the pair count is a 64-bit atomic), the tasks follow them
-__host__ __device__ inline size_t plan_counter_offset(int H) { return ((size_t)H * (kC + 1) + 3) & ~(size_t)3; }
+// Layout of the plan (an int32 array owned by a structure snapshot): first row of every key cluster in kp / vp,
+// one bit per key cluster saying whether it holds any token, the counters (on a 16-byte boundary: the pair
+// count is a 64-bit atomic), the tasks, and the union length of every query cluster.
+__host__ __device__ inline size_t plan_nonempty_offset(int H) { return (size_t)H * (kC + 1); }
+__host__ __device__ inline size_t plan_counter_offset(int H) { return (plan_nonempty_offset(H) + (size_t)H * (kC / 32) + 3) & ~(size_t)3; }
 __host__ __device__ inline size_t plan_task_offset(int H) { return plan_counter_offset(H) + PLAN_HDR; }
-__host__ __device__ inline size_t plan_max_tasks(int H, int N, int CQ) { return (size_t)H * (CQ + cdiv(N, QT) + 1); }
+__host__ __device__ inline size_t plan_max_tasks(int H, int N, int CQ) { return (size_t)H * (CQ + cdiv(N, TASK_ROWS) + 1); }
 
 struct PlanView {
-  int* k_off;      // [H][C + 1]
-  int* counters;   // [PLAN_HDR]
-  int4* tasks;     // (head, query cluster, first sorted row, rows)
-  int* kv_lens;    // [H][CQ]
+  int* k_off;           // [H][C + 1]
+  uint32_t* nonempty;   // [H][C / 32]
+  int* counters;        // [PLAN_HDR]
+  int4* tasks;          // (head, query cluster, first sorted row, rows)
+  int* kv_lens;         // [H][CQ]
 };
 __host__ __device__ inline PlanView plan_view(int* plan, int H, int N, int CQ) {
   PlanView v;
   v.k_off = plan;
+  v.nonempty = reinterpret_cast<uint32_t*>(plan + plan_nonempty_offset(H));
   v.counters = plan + plan_counter_offset(H);
   v.tasks = reinterpret_cast<int4*>(plan + plan_task_offset(H));
   v.kv_lens = plan + plan_task_offset(H) + 4 * plan_max_tasks(H, N, CQ);
@@ -64,132 +71,146 @@ __device__ __forceinline__ float ex2_approx(float x) {
 }
 
 // ---------------------------------------------------------------------------
-// plan
+// plan: key-cluster offsets, union lengths, tasks (most work first inside a head)
 // ---------------------------------------------------------------------------
-// tokens in the union of every query cluster (0 for an empty query cluster)
-__global__ void __launch_bounds__(256) kvlen_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz,
-                                                    const uint32_t* __restrict__ ub, int* __restrict__ kv_lens,
-                                                    int CQ) {
-  const int h = blockIdx.y, c = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (c >= CQ) return;
-  int total = 0;
-  if (qsz[(size_t)h * CQ + c] > 0) {
-    const uint32_t* words = ub + ((size_t)h * CQ + c) * (kC / 32);
-    for (int w = lane; w < kC / 32; w += 32) {
-      uint32_t bits = words[w];
-      while (bits) {
-        const int b = __ffs(bits) - 1;
-        total += ksz[(size_t)h * kC + w * 32 + b];
-        bits &= bits - 1;
-      }
-    }
-  }
-  total = __reduce_add_sync(0xffffffffu, total);
-  if (lane == 0) kv_lens[(size_t)h * CQ + c] = total;
-}
-
-__device__ __forceinline__ int block_excl_scan_256(int v, int* ws, int& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Exclusive prefix of v over the 256 threads of the CTA (every thread calls it); scratch holds 8 ints.
+__device__ __forceinline__ int block_prefix_256(int v, int* scratch, int& total) {
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   const int inc = warp_incl_scan(v, lane);
   __syncthreads();
-  if (lane == 31) ws[warp] = inc;
+  if (lane == 31) scratch[w] = inc;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    for (int i = 0; i < 8; ++i) { const int t = ws[i]; ws[i] = acc; acc += t; }
-    ws[8] = acc;
+  int before = 0, all = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int part = scratch[i];
+    before += i < w ? part : 0;
+    all += part;
   }
-  __syncthreads();
-  total = ws[8];
-  return inc - v + ws[warp];
+  total = all;
+  return before + inc - v;
 }
 
-// One CTA per head: key-cluster offsets, tasks of at most TASK_ROWS rows (a larger query cluster
-// gives full tasks and one remainder task), longest-processing-time order inside the head.
-__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qsz, const int* __restrict__ ksz, int H,
-                                                   int N, int CQ, int* __restrict__ plan) {
-  __shared__ int ws[16];
-  __shared__ unsigned long long skey[PLAN_SORT_MAX];
+// One CTA per head.  A query cluster of n rows gives ceil(n / TASK_ROWS) tasks: full ones first, the remainder
+// last (a remainder of at most QT rows costs one row tile instead of two).
+__global__ void __launch_bounds__(256) plan_kernel(const int* __restrict__ qcount, const int* __restrict__ kcount,
+                                                   const uint32_t* __restrict__ ubits, int H, int N, int CQ,
+                                                   int* __restrict__ plan) {
+  __shared__ int s_off[kC + 1];
+  __shared__ unsigned long long s_key[PLAN_SORT_MAX];
+  __shared__ int s_scan[8];
   const PlanView pv = plan_view(plan, H, N, CQ);
-  const int h = blockIdx.x, tid = threadIdx.x;
+  const int h = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  int running = 0;
-  for (int base = 0; base < kC; base += 256) {
-    const int v = ksz[(size_t)h * kC + base + tid];
-    int tot;
-    const int ex = block_excl_scan_256(v, ws, tot);
-    pv.k_off[(size_t)h * (kC + 1) + base + tid] = running + ex;
-    running += tot;
+  // first kp / vp row of every key cluster (eight consecutive clusters per thread) and the non-empty bits
+  {
+    int c8[8], sum = 0;
+    uint32_t some = 0u;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      c8[i] = kcount[(size_t)h * kC + tid * 8 + i];
+      sum += c8[i];
+      some |= (c8[i] > 0 ? 1u : 0u) << i;
+    }
+    int total;
+    int run = block_prefix_256(sum, s_scan, total);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { s_off[tid * 8 + i] = run; run += c8[i]; }
+    if (tid == 255) s_off[kC] = run;
+    // four neighbouring threads hold the four bytes of one 32-cluster word
+    uint32_t word = some << (8 * (tid & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);
+    if ((tid & 3) == 0) pv.nonempty[(size_t)h * (kC / 32) + (tid >> 2)] = word;
   }
-  if (tid == 0) pv.k_off[(size_t)h * (kC + 1) + kC] = running;
+  __syncthreads();
+  for (int i = tid; i <= kC; i += 256) pv.k_off[(size_t)h * (kC + 1) + i] = s_off[i];
 
-  // tasks of the heads before this one, so the task array is head-major
-  int gbase = 0, ntask = 0;
+  // tokens in the union of every query cluster (a warp per cluster), and the pairs the head executes
+  unsigned long long pairs = 0;
+  for (int c = warp; c < CQ; c += 8) {
+    const int n = qcount[(size_t)h * CQ + c];
+    int len = 0;
+    if (n > 0) {
+      const uint32_t* words = ubits + ((size_t)h * CQ + c) * (kC / 32);
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int w = lane + 32 * half;
+        for (uint32_t bits = words[w]; bits; bits &= bits - 1) {
+          const int cl = w * 32 + __ffs(bits) - 1;
+          len += s_off[cl + 1] - s_off[cl];
+        }
+      }
+    }
+    len = __reduce_add_sync(0xffffffffu, len);
+    if (lane == 0) {
+      pv.kv_lens[(size_t)h * CQ + c] = len;
+      pairs += (unsigned long long)n * (unsigned long long)len;
+    }
+  }
+  if (lane == 0 && pairs) atomicAdd(reinterpret_cast<unsigned long long*>(pv.counters + 2), pairs);
+  __syncthreads();
+
+  // the task array is head-major (the K / V rows of a head stay in L2 while its unions are read):
+  // count the tasks of the heads before this one
+  int first = 0, mine = 0;
   for (int hh = 0; hh <= h; ++hh) {
     int cnt = 0;
-    for (int c = tid; c < CQ; c += 256) cnt += cdiv(qsz[(size_t)hh * CQ + c], TASK_ROWS);
-    int tot;
-    block_excl_scan_256(cnt, ws, tot);
-    if (hh < h) gbase += tot; else ntask = tot;
+    for (int c = tid; c < CQ; c += 256) cnt += cdiv(qcount[(size_t)hh * CQ + c], TASK_ROWS);
+    int total;
+    block_prefix_256(cnt, s_scan, total);
+    if (hh < h) first += total; else mine = total;
   }
-  if (h == H - 1 && tid == 0) pv.counters[0] = gbase + ntask;
+  if (h == H - 1 && tid == 0) pv.counters[0] = first + mine;
 
-  int qrun = 0, trun = 0;
-  unsigned long long pairs = 0;
-  for (int base = 0; base < CQ; base += 256) {
-    const int c = base + tid;
-    const int v = c < CQ ? qsz[(size_t)h * CQ + c] : 0;
-    const int nt = cdiv(v, TASK_ROWS);
-    int totq, tott;
-    const int exq = block_excl_scan_256(v, ws, totq);
-    const int ext = block_excl_scan_256(nt, ws, tott);
-    int s = qrun + exq;
-    for (int i = 0; i < nt; ++i) {
-      // full tasks first, the remainder last: a remainder of at most QT rows costs one row tile instead of two
-      const int rows = i + 1 < nt ? TASK_ROWS : v - (nt - 1) * TASK_ROWS;
-      pv.tasks[gbase + trun + ext + i] = make_int4(h, c, s, rows);
-      s += rows;
-    }
-    if (c < CQ) pairs += (unsigned long long)v * (unsigned long long)pv.kv_lens[(size_t)h * CQ + c];
-    qrun += totq;
-    trun += tott;
+  int rows_before = 0, tasks_before = 0;
+  for (int c0 = 0; c0 < CQ; c0 += 256) {
+    const int c = c0 + tid;
+    const int n = c < CQ ? qcount[(size_t)h * CQ + c] : 0;
+    const int nt = cdiv(n, TASK_ROWS);
+    int tot_rows, tot_tasks;
+    const int row0 = rows_before + block_prefix_256(n, s_scan, tot_rows);
+    const int task0 = tasks_before + block_prefix_256(nt, s_scan, tot_tasks);
+    for (int i = 0; i < nt; ++i)
+      pv.tasks[first + task0 + i] = make_int4(h, c, row0 + i * TASK_ROWS, min(TASK_ROWS, n - i * TASK_ROWS));
+    rows_before += tot_rows;
+    tasks_before += tot_tasks;
   }
-  atomicAdd(reinterpret_cast<unsigned long long*>(pv.counters + 2), pairs);
   __syncthreads();
-  if (ntask > PLAN_SORT_MAX || ntask < 2) return;
+  if (mine < 2 || mine > PLAN_SORT_MAX) return;
 
-  int P2 = 2;
-  while (P2 < ntask) P2 <<= 1;
-  for (int i = tid; i < P2; i += 256) {
+  // most work first (rows x union length); equal work keeps its order
+  int pow2 = 2;
+  while (pow2 < mine) pow2 <<= 1;
+  for (int i = tid; i < pow2; i += 256) {
     unsigned long long key = 0ull;
-    if (i < ntask) {
-      const int4 tk = pv.tasks[gbase + i];
-      unsigned long long work = (unsigned long long)tk.w * (unsigned long long)pv.kv_lens[(size_t)h * CQ + tk.y];
-      if (work > 0xFFFFFFFFull) work = 0xFFFFFFFFull;
-      key = (work << 32) | (unsigned long long)(0x7FFFFFFF - i);
+    if (i < mine) {
+      const int4 t = pv.tasks[first + i];
+      const unsigned long long work = min((unsigned long long)t.w * (unsigned long long)pv.kv_lens[(size_t)h * CQ + t.y], 0xFFFFFFFFull);
+      key = (work << 32) | (unsigned long long)(0xFFFFFFFFu - (unsigned)i);
     }
-    skey[i] = key;
+    s_key[i] = key;
   }
   __syncthreads();
-  for (int k = 2; k <= P2; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < P2; i += 256) {
-        const int ixj = i ^ j;
-        if (ixj > i) {
-          const unsigned long long a = skey[i], b = skey[ixj];
-          const bool desc = (i & k) == 0;
-          if (desc ? (a < b) : (a > b)) { skey[i] = b; skey[ixj] = a; }
+  for (int span = 2; span <= pow2; span <<= 1) {
+    for (int step = span >> 1; step > 0; step >>= 1) {
+      for (int i = tid; i < pow2; i += 256) {
+        const int j = i ^ step;
+        if (j > i) {
+          const unsigned long long x = s_key[i], y = s_key[j];
+          const bool descending = (i & span) == 0;
+          if (descending ? x < y : x > y) { s_key[i] = y; s_key[j] = x; }
         }
       }
       __syncthreads();
     }
   }
-  int4 mine[PLAN_SORT_MAX / 256];
-  int n = 0;
-  for (int i = tid; i < ntask; i += 256) mine[n++] = pv.tasks[gbase + (0x7FFFFFFF - (int)(skey[i] & 0xFFFFFFFFull))];
+  int4 keep[PLAN_SORT_MAX / 256];
+  int k = 0;
+  for (int i = tid; i < mine; i += 256) keep[k++] = pv.tasks[first + (int)(0xFFFFFFFFu - (unsigned)(s_key[i] & 0xFFFFFFFFull))];
   __syncthreads();
-  n = 0;
-  for (int i = tid; i < ntask; i += 256) pv.tasks[gbase + i] = mine[n++];
+  k = 0;
+  for (int i = tid; i < mine; i += 256) pv.tasks[first + i] = keep[k++];
 }
 
 __global__ void plan_info_kernel(const int* __restrict__ counters, int* __restrict__ info) {
@@ -219,57 +240,51 @@ __device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
   }
 }
 
-// Runs of selected, non-empty key clusters of one union, as (first kp/vp row, first position in the
-// union) pairs in sRunStart / sRunCum (sRunCum[runs] = union length) and the run count in sMisc[1].
-// Called by every thread of the CTA (it contains two CTA-wide barriers); threads 0..127 hold 16 key
-// clusters each.  Returns false when the run list would not fit (the abort flag is then set).
+// The union of one task as runs of consecutive kp / vp rows: maximal stretches of selected, non-empty key
+// clusters that follow each other.  sRunStart[r] = first row of run r, sRunCum[r] = position of its first
+// token in the union, sRunCum[runs] = union length, sMisc[1] = runs.  Warp 0 does the work with the bitmap as
+// 64-bit words (two bitmap words per lane): a run starts at a set bit whose lower neighbour is clear and ends
+// at a set bit whose upper neighbour is clear, so the r-th start and the r-th end delimit run r.  Called by
+// every thread of the CTA (it ends with a CTA-wide barrier).  Returns false when the run list would not fit
+// (the abort flag is then set).
 __device__ __forceinline__ bool build_runs(const int* __restrict__ koh, const uint32_t* __restrict__ ubr,
-                                           int* sRunStart, int* sRunCum, int* sMisc, volatile int* abort_flag,
-                                           int* status) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const bool scan = tid < 128;
-  const int c0 = scan ? tid * 16 : 0;
-  const uint32_t bw = scan ? (ubr[c0 >> 5] >> (c0 & 31)) & 0xFFFFu : 0u;
-  const int base0 = koh[c0];
-  bool pne0 = false;
-  if (scan && c0 > 0) pne0 = ((ubr[(c0 - 1) >> 5] >> ((c0 - 1) & 31)) & 1u) && base0 > koh[c0 - 1];
-  int offs[17];
-  offs[0] = base0;
-#pragma unroll
-  for (int j = 0; j < 16; ++j) offs[j + 1] = koh[c0 + j + 1];
-  int cnt = 0, sz = 0;
-  {
-    bool pne = pne0;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-      if (cne) { if (!pne) ++cnt; sz += offs[j + 1] - offs[j]; }
-      pne = cne;
-    }
-  }
-  // exclusive scans of (cnt, sz) over the 128 scanning threads
-  int* ws = sMisc + 8;
-  const int ic = warp_incl_scan(cnt, lane), is = warp_incl_scan(sz, lane);
-  if (scan && lane == 31) { ws[warp] = ic; ws[4 + warp] = is; }
-  __syncthreads();
-  int kbase = ic - cnt, pbase = is - sz;
-  for (int w = 0; w < warp && w < 4; ++w) { kbase += ws[w]; pbase += ws[4 + w]; }
-  const int totc = ws[0] + ws[1] + ws[2] + ws[3];
-  if (totc > MAX_RUNS) {   // cannot happen for C = 2048; guard the static arrays anyway
-    if (tid == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
-  } else if (scan) {
-    bool pne = pne0;
-    int k = kbase, p = pbase;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const bool cne = ((bw >> j) & 1u) && offs[j + 1] > offs[j];
-      if (cne) {
-        if (!pne) { sRunStart[k] = offs[j]; sRunCum[k] = p; ++k; }
-        p += offs[j + 1] - offs[j];
+                                           const uint32_t* __restrict__ nonempty, int* sRunStart, int* sRunCum,
+                                           int* sMisc, volatile int* abort_flag, int* status) {
+  const int lane = threadIdx.x & 31;
+  if ((threadIdx.x >> 5) == 0) {
+    const unsigned long long sel = ((unsigned long long)(ubr[2 * lane + 1] & nonempty[2 * lane + 1]) << 32) |
+                                   (unsigned long long)(ubr[2 * lane] & nonempty[2 * lane]);
+    // neighbours across the lane boundary
+    const unsigned long long below = __shfl_up_sync(0xffffffffu, sel, 1), above = __shfl_down_sync(0xffffffffu, sel, 1);
+    const unsigned long long carry_in = lane > 0 ? below >> 63 : 0ull;
+    const unsigned long long carry_out = lane < 31 ? (above & 1ull) << 63 : 0ull;
+    unsigned long long starts = sel & ~((sel << 1) | carry_in);
+    unsigned long long ends = sel & ~((sel >> 1) | carry_out);
+    const int mine = __popcll(starts);
+    const int before_s = warp_incl_scan(mine, lane) - mine;
+    const int before_e = warp_incl_scan(__popcll(ends), lane) - __popcll(ends);
+    const int runs = __shfl_sync(0xffffffffu, before_s + mine, 31);
+    if (runs > MAX_RUNS) {      // cannot happen for C = 2048; guard the static arrays anyway
+      if (lane == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
+    } else {
+      int r = before_s;
+      for (; starts; starts &= starts - 1) sRunStart[r++] = koh[64 * lane + __ffsll((long long)starts) - 1];
+      r = before_e;
+      for (; ends; ends &= ends - 1) sRunCum[r++] = koh[64 * lane + __ffsll((long long)ends)];      // one past the run's last row
+      __syncwarp();
+      // lengths -> positions: every lane turns a block of consecutive runs into a running sum
+      const int per = (runs + 31) >> 5, lo = min(lane * per, runs), hi = min(lo + per, runs);
+      int sum = 0;
+      for (int i = lo; i < hi; ++i) sum += sRunCum[i] - sRunStart[i];
+      int pos = warp_incl_scan(sum, lane) - sum;
+      const int total = __shfl_sync(0xffffffffu, pos + sum, 31);
+      for (int i = lo; i < hi; ++i) {
+        const int len = sRunCum[i] - sRunStart[i];
+        sRunCum[i] = pos;
+        pos += len;
       }
-      pne = cne;
+      if (lane == 0) { sRunCum[runs] = total; sMisc[1] = runs; }
     }
-    if (tid == 127) { sRunCum[k] = p; sMisc[1] = totc; }
   }
   __syncthreads();
   return *abort_flag == 0;
@@ -363,8 +378,8 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     sQidx[tid] = h * N + qperm[rowbase + (tid < qrows ? tid : 0)];
 
     // ---- runs of selected, non-empty key clusters -----------------------------
-    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32), sRunStart, sRunCum, sMisc,
-                    abort_flag, status))
+    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
+                    pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
       break;
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
@@ -710,8 +725,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
     }
 
     // ---- runs of selected, non-empty key clusters ------------------------------------------------
-    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32), sRunStart, sRunCum, sMisc,
-                    abort_flag, status))
+    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
+                    pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
       break;
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
@@ -1214,6 +1229,59 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
 
 using namespace t2t;
 
+namespace {
+// Launch facts that do not change between calls: looked up (and the kernels' shared-memory limits raised)
+// once per device and process, not on every call.
+struct DeviceFacts {
+  bool ready;
+  int sms;
+};
+std::mutex g_facts_mutex;
+const DeviceFacts* device_facts() {
+  static DeviceFacts table[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(g_facts_mutex);
+  DeviceFacts* f = &table[dev];
+  if (!f->ready) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return nullptr;
+    if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(attn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM) != cudaSuccess ||
+        cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
+      return nullptr;
+    f->sms = sms;
+    f->ready = true;
+  }
+  return f;
+}
+
+// Tensor maps are pure functions of (base address, rows, box rows): the operator passes the same few buffers on
+// every call, so the last encodings are kept.
+struct MapSlot {
+  const void* base;
+  uint64_t rows;
+  uint32_t box_rows;
+  CUtensorMap map;
+};
+std::mutex g_map_mutex;
+bool cached_row_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows) {
+  static MapSlot slots[16] = {};
+  static unsigned next = 0;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  for (const MapSlot& s : slots)
+    if (s.base == base && s.rows == rows && s.box_rows == box_rows && s.base != nullptr) { *out = s.map; return true; }
+  MapSlot fresh;
+  fresh.base = base;
+  fresh.rows = rows;
+  fresh.box_rows = box_rows;
+  if (!make_row_tile_map(&fresh.map, base, rows, box_rows)) return false;
+  slots[next++ % 16] = fresh;
+  *out = fresh.map;
+  return true;
+}
+}  // namespace
+
 extern "C" size_t t2t_tile_attn_plan_ints(int H, int N, int CQ) {
   return plan_task_offset(H) + 4 * plan_max_tasks(H, N, CQ) + (size_t)H * CQ;
 }
@@ -1232,9 +1300,7 @@ extern "C" int t2t_tile_attn_plan(const void* tile_sizes, const void* kcounts, c
   if (!tile_sizes || !kcounts || !unip || !plan || H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
   const PlanView pv = plan_view(plan, H, N, CQ);
   if (cudaMemsetAsync(pv.counters, 0, PLAN_HDR * sizeof(int), st) != cudaSuccess) return T2T_ERR_CUDA;
-  kvlen_kernel<<<dim3(cdiv(CQ, 8), H), 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts,
-                                                     (const uint32_t*)unip, pv.kv_lens, CQ);
-  plan_kernel<<<H, 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts, H, N, CQ, plan);
+  plan_kernel<<<H, 256, 0, st>>>((const int*)tile_sizes, (const int*)kcounts, (const uint32_t*)unip, H, N, CQ, plan);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
 
@@ -1251,17 +1317,13 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   if (cudaMemsetAsync(pv.counters + 1, 0, sizeof(int), st) != cudaSuccess ||
       cudaMemsetAsync(pv.counters + 4, 0, sizeof(int), st) != cudaSuccess)
     return T2T_ERR_CUDA;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
-      cudaFuncSetAttribute(attn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM) != cudaSuccess)
-    return T2T_ERR_CUDA;
+  const DeviceFacts* facts = device_facts();
+  if (!facts) return T2T_ERR_CUDA;
+  const int sms = facts->sms;
   // tensor maps over q, kp, vp as [H * N, 128] matrices: the kernel fetches tile rows four at a time
   CUtensorMap mq, mk, mv;
   const uint64_t rows = (uint64_t)H * (uint64_t)N;
-  if (!make_row_gather_map(&mq, q, rows) || !make_row_gather_map(&mk, kp, rows) ||
-      !make_row_gather_map(&mv, vp, rows))
+  if (!cached_row_map(&mq, q, rows, 1) || !cached_row_map(&mk, kp, rows, 1) || !cached_row_map(&mv, vp, rows, 1))
     return T2T_ERR_CUDA;
   // tasks above 128 rows first (one CTA per SM, two row tiles per K/V stream), then the others
   attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out,
@@ -1297,11 +1359,10 @@ extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* 
   __nv_bfloat16* attn_out;
   float* attn_lse;
   split_ws(ws, H, N, &attn_out, &attn_lse);
-  if (cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
-    return T2T_ERR_CUDA;
+  if (!device_facts()) return T2T_ERR_CUDA;
   // the value sums as an [H * 2048, 128] matrix, fetched 64 rows x 64 columns at a time
   CUtensorMap msv;
-  if (!make_row_tile_map(&msv, sumv, (uint64_t)H * kC, TL_H)) return T2T_ERR_CUDA;
+  if (!cached_row_map(&msv, sumv, (uint64_t)H * kC, TL_H)) return T2T_ERR_CUDA;
   tail_kernel<<<dim3(cdiv(N, TL_Q), H), TL_THREADS, TL_SMEM, st>>>(
       msv, attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
       (__nv_bfloat16*)out, N, CQ, d_status);
