@@ -34,8 +34,9 @@ sys.path.insert(0, str(ROOT))
 
 WORKLOAD = dict(name="wan2.1-14b-720p-self-attention-layer", H=40, grid="720p", N=75600, CQ=512, D=128,
                 s_frac=0.015)
-KERNELS_REBUILD = 2 + 21 + 3 + 1 + 2 + 3  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), centroid moments+select+fix, gather, plan, attention (two kernels) + merge
+KERNELS_REBUILD = 2 + 21 + 3 + 1 + 1 + 3  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), centroid moments+select+fix, gather, plan, attention (two kernels) + merge
 KERNELS_REUSE = 1 + 1 + 3 + 3   # project q, gather k, value stats, attention (two kernels) + merge
+ATTN_DRAM_BYTES_480P_8H = 381.2e6      # attn2_kernel + attn_kernel, H 8, N 32,760 (ncu)
 METRIC = "t2t_attn_ms_per_layer"
 UNIT = "ms/layer"
 
@@ -100,9 +101,10 @@ def time_events(fn, steps, stream=None):
     return e0.elapsed_time(e1)
 
 
-def dense_attention_ms(q, k, v):
-    """Fastest dense attention on this box for the same tensors: median of 3
-    timed calls after 2 warm-ups, per library."""
+def dense_attention_ms(q, k, v, warm=3, timed=10):
+    """Fastest dense attention on this box for the same tensors: per library the
+    median of `timed` calls (each timed on its own by CUDA events) after `warm`
+    warm-ups."""
     import torch.nn.functional as F
     out = {}
     qb, kb, vb = q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0)
@@ -130,10 +132,10 @@ def dense_attention_ms(q, k, v):
         pass
     for name, run in cands.items():
         try:
-            for _ in range(2):
+            for _ in range(warm):
                 run()
-            ts = sorted(time_events(run, 1) for _ in range(3))
-            out[name] = ts[1]
+            ts = sorted(time_events(run, 1) for _ in range(timed))
+            out[name] = ts[len(ts) // 2]
         except Exception as exc:      # noqa: BLE001 - a backend may refuse the shape
             out[name] = None
             print(f"[bench] dense backend {name} unavailable: {type(exc).__name__}", file=sys.stderr)
@@ -204,6 +206,57 @@ def run_reference(args, rank):
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
+
+def layer_480p(dev, lo, hi, maxr, barrier):
+    """The 480p layer (N 32,760, CQ 256) for this rank's heads: rebuild and reuse call times at the 1.5 % and
+    5 % budgets, the fastest dense attention on the same tensors and the relative L2 distance from it."""
+    from token2tile_b200 import MaskedStepDeploy
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    import torch.nn.functional as F
+    N, CQ = 32760, 256
+    q, k, v = (t.to(dev) for t in locality_mixture(hi - lo, GRIDS["480p"], heads=range(lo, hi)))
+    dense = dense_attention_ms(q, k, v, warm=2, timed=5)
+    dense_ok = [t for t in dense.values() if t]
+    dense_best = maxr(min(dense_ok)) if dense_ok else None
+    dense_out = F.scaled_dot_product_attention(q.unsqueeze(0), k.unsqueeze(0), v.unsqueeze(0))[0].float()
+    out = {"N": N, "CQ": CQ, "heads_per_gpu": hi - lo, "dense_ms": dense, "fastest_dense_ms": dense_best, "budgets": {}}
+    for frac in (0.015, 0.05):
+        op = MaskedStepDeploy(hi - lo, N, CQ, s_frac=frac, device=dev, mask_refresh=4)
+        state = op.init_state(q, k, warm_iters=4, seed=0)
+
+        clock = [0]
+
+        def rebuild():
+            clock[0] += 4                          # a refresh period later: branch 0 rebuilds
+            op.set_cfg_call(0, key=0, step=clock[0])
+            op.step(q, k, v, state)
+
+        def reuse():
+            op.set_cfg_call(1, key=0, step=clock[0])
+            op.step(q, k, v, state)
+
+        for _ in range(3):
+            rebuild()
+        barrier()
+        rb = maxr(time_events(rebuild, 5) / 5)
+        assert op.last_rebuilt is True
+        clock[0] += 4
+        op.set_cfg_call(0, key=0, step=clock[0])
+        res = op.step(q, k, v, state).float()
+        rel = float(((res - dense_out).norm() / dense_out.norm()).item())
+        reuse()
+        barrier()
+        ru = maxr(time_events(reuse, 5) / 5)
+        assert op.last_rebuilt is False and op.device_status() == 0
+        amort = (rb + 7 * ru) / 8
+        out["budgets"][f"{frac * 100:g}%"] = {
+            "ns": op.ns, "rebuild_ms": rb, "reuse_ms": ru, "amortised_ms_1_rebuild_7_reuse": amort,
+            "rel_l2_vs_dense": maxr(rel),
+            "speedup_vs_dense": {"rebuild": dense_best / rb, "reuse": dense_best / ru, "amortised": dense_best / amort}
+            if dense_best else None}
+        del op, state, res
+    return out
+
 
 def run_ours(args, rank, world, local_rank):
     from token2tile_b200 import MaskedStepDeploy
@@ -395,16 +448,26 @@ def run_ours(args, rank, world, local_rank):
     except Exception as exc:      # noqa: BLE001
         print(f"[bench] init timing skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
 
+    # BASELINE configuration 2: the 480p layer (32,760 tokens, 256 query clusters), budgets 1.5 % and 5 %
+    config2 = None
+    if not (args.heads or args.grid):
+        try:
+            del qd, kd, vd, hq, hk, hv, hout
+            torch.cuda.empty_cache()
+            config2 = layer_480p(dev, lo, hi, maxr, barrier)
+        except Exception as exc:      # noqa: BLE001 - a second, informative measurement
+            print(f"[bench] 480p configuration skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
+
     pk = peaks()
     flops = 4.0 * W["D"] * pairs
     t_attn = stages.get("attn_exact", 0.0)
     roofline = None
     if t_attn > 0:
         ach = flops / (t_attn * 1e-3) / 1e12
-        # DRAM bytes of the two attention kernels: 381.2 MB (dram__bytes_read + write) in the ncu capture of the
-        # 8-head 480p case (profiles/attn_kernels_480p_8heads.md), scaled by the rows processed (each kernel
-        # reads q, kp, vp once; the exact output is written once: traffic is proportional to H * N)
-        traffic = 381.2e6 * (Hl * float(N)) / (8 * 32760.0)
+        # DRAM bytes of the two attention kernels: dram__bytes_read + dram__bytes_write of one ncu capture of the
+        # 8-head 480p case, scaled by the rows processed (each kernel reads q, kp, vp once; the exact output is
+        # written once: traffic is proportional to H * N)
+        traffic = ATTN_DRAM_BYTES_480P_8H * (Hl * float(N)) / (8 * 32760.0)
         roofline = {"kernel": "attn2_kernel + attn_kernel (exact tile attention)", "bound": "tensor", "achieved": ach, "peak": pk["tf"],
                     "unit": "TFLOP/s", "frac": ach / pk["tf"], "traffic": traffic,
                     "traffic_source": "ncu 480p x 8 heads capture scaled by rows", "peak_source": pk["src"] +
@@ -417,9 +480,32 @@ def run_ours(args, rank, world, local_rank):
         "kmeans": (6 * N * 32 * B + 2 * N * W["D"] * B + 10 * N * 4) * Hl,
         "vstats": 2 * N * W["D"] * B * Hl,
     }
-    stage_roof = {n: {"ms": stages[n], "algorithmic_GBps": stage_bytes[n] / (stages[n] * 1e-3) / 1e9,
-                      "frac_of_hbm_peak": stage_bytes[n] / (stages[n] * 1e-3) / 1e9 / pk["hbm"]}
-                  for n in stage_bytes if stages.get(n)}
+    # gather_k and vstats are timed in the reuse call, where they run alone on the main stream (in a rebuild
+    # call the key gather runs on the side stream under the selection and the value statistics are part of
+    # the clustering stage)
+    stage_ms = dict(stages)
+    for n in ("gather_k", "vstats"):
+        if reuse_stages.get(n):
+            stage_ms[n] = reuse_stages[n]
+    stage_roof = {}
+    for n in stage_bytes:
+        if stage_ms.get(n):
+            gbs = stage_bytes[n] / (stage_ms[n] * 1e-3) / 1e9
+            if gbs <= 1.05 * pk["hbm"]:          # anything above the copy peak is a timing artefact, not a result
+                stage_roof[n] = {"ms": stage_ms[n], "algorithmic_GBps": gbs, "frac_of_hbm_peak": gbs / pk["hbm"],
+                                 "timed_in": "reuse call" if n in ("gather_k", "vstats") else "rebuild call"}
+    if stages.get("select"):
+        # scoring + selection: N * C scores per head; bound by integer / compare issue, so both nominal
+        # fractions are reported next to the score rate
+        t_sel = stages["select"] * 1e-3
+        scores = float(N) * 2048 * Hl
+        sel_bytes = (N * 32 * B + 2048 * 32 * B + CQ * 2048 / 8) * Hl
+        stage_roof["select"] = {"ms": stages["select"], "scores_per_s": scores / t_sel,
+                                "TFLOPs": 2 * 32 * scores / t_sel / 1e12,
+                                "frac_of_tensor_peak": 2 * 32 * scores / t_sel / 1e12 / pk["tf"],
+                                "algorithmic_GBps": sel_bytes / t_sel / 1e9,
+                                "frac_of_hbm_peak": sel_bytes / t_sel / 1e9 / pk["hbm"],
+                                "bound": "integer / compare instruction issue (about 27 instructions per score)"}
     tail_flops = float(N) * 2048 * (2 * 32 + 2 * W["D"]) * Hl
     if stages.get("residual_merge"):
         stage_roof["residual_merge"] = {"ms": stages["residual_merge"],
@@ -431,7 +517,8 @@ def run_ours(args, rank, world, local_rank):
         step, cores = cpu_head_step_factory()
         val = step()
         cpu = {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
-               "sample": "one head of 40 (full 75,600 tokens), one rebuild call, time x 40"}
+               "sample": "one head of 40 (full 75,600 tokens), one rebuild call, time x 40 (an extrapolation; "
+                         "cpu_config below is measured whole)"}
         try:      # the CPU-sized configuration as a whole: H 2, N 4096, CQ 32, fp32, 5 % budget
             cpu["cpu_config"] = cpu_small_config()
         except Exception as exc:      # noqa: BLE001 - informative only
@@ -450,12 +537,14 @@ def run_ours(args, rank, world, local_rank):
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
                     "d2h_bytes_per_step": Hl * N * W["D"] * 2,
+                    "h2d_GBps_this_rank": bytes_in / (e2e_ms * 1e-3) / 1e9,
                     "mode": "double-buffered inputs and outputs: the copies of a step overlap the neighbouring steps' compute",
                     "serial_ms": e2e_serial_ms},
             "gpu_launches": KERNELS_REBUILD * args.steps, "clocks": clocks,
             "reuse_ms": reuse_ms, "amortised_ms_1_rebuild_7_reuse": amort, "stages_ms": stages,
             "reuse_stages_ms": reuse_stages, "stage_roofline": stage_roof, "tasks": tasks,
             "dense_ms": dense, "fastest_dense_ms": dense_best, "budgets": budgets, "init_ms": init_ms,
+            "config_480p": config2,
             "speedup_vs_dense": {"rebuild": dense_best / ms_step, "reuse": dense_best / reuse_ms,
                                  "amortised": dense_best / amort} if dense_best else None,
         }

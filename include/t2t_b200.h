@@ -119,8 +119,11 @@ int t2t_vstats_gather(const void* V, const void* kperm, const void* kcounts, voi
  * inside the library image, T2T_STATIC_VSTATS_MAX_HC * 516 bytes (about 4 MB)
  * resident on every GPU that loads the library, for as long as the process
  * lives.  Inputs and outputs are still the caller's.  Limits and rules:
- *   - H * C must not exceed T2T_STATIC_VSTATS_MAX_HC (4 heads of 2048
- *     clusters); larger shapes return T2T_ERR_TOO_LARGE and launch nothing;
+ *   - two limits, both checked before anything is launched: H must not exceed
+ *     T2T_STATIC_VSTATS_MAX_HC / 2048 = 4 heads (the per-head block maxima
+ *     have room for that many), and H * C must not exceed
+ *     T2T_STATIC_VSTATS_MAX_HC (so 4 heads of 2048 clusters fit, 8 heads of
+ *     1024 do not); anything larger returns T2T_ERR_TOO_LARGE;
  *   - the first call on each device looks up the array's device address (with
  *     that device current); make that first call outside any stream capture;
  *   - all calls share the one array and it keeps the last call's contents; the

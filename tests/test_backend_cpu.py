@@ -40,6 +40,9 @@ class FakeDeploy:
     def reset_cfg_reuse(self):
         self.resets += 1
 
+    def check_status(self, wait=True):
+        self.status_checks = getattr(self, "status_checks", 0) + 1
+
     def step(self, q, k, v, state):
         assert q.dtype == torch.bfloat16 and q.is_contiguous() and q.shape == (self.H, self.N, 128)
         self.calls.append(dict(cfg=self._next, ns=int(self.ns_t)))
@@ -224,6 +227,7 @@ def test_new_request_resets_snapshots_and_runtime_is_shared():
     assert dep.resets == 1
     a.forward(q, k, v, manual_meta(c2, 5))
     assert dep.resets == 2 and len(FakeDeploy.instances) == 1
+    assert dep.status_checks == 2                # the device status word is examined at every request boundary
     # a request may not change geometry or settings half-way
     with pytest.raises(RuntimeError, match="geometry changed"):
         a.forward(q, k, v, manual_meta(c2, 6, mask_refresh=2))
@@ -354,16 +358,17 @@ def test_video_tokens_from_published_layout_and_condition_rows():
     used = 80
     layout = {"video": 56, "video_start": 24, "video_stop": 80}
     B.set_forward_context(SimpleNamespace(current_timestep=12, minimax_h3_layout=layout))
-    assert B._h3_video_tokens_from_layout(used) == 56
-    assert B._h3_video_tokens_from_layout(81) == 0                      # not the main document
+    cpu = torch.device("cpu")
+    assert B._h3_split(used, "dense", cpu) == (56, None)
+    assert B._h3_split(81, "dense", cpu) == (0, None)                    # not the main document
     layout2 = {"video": 56, "video_start": 10, "video_stop": 80}
     B.set_forward_context(SimpleNamespace(current_timestep=12, minimax_h3_layout=layout2))
-    assert B._h3_video_tokens_from_layout(used) == 0                    # video is not the contiguous tail
+    assert B._h3_split(used, "dense", cpu) == (0, None)                  # video is not the contiguous tail
     # condition frames precede the audio rows: only the generated tail is sparse
     layout3 = {"video": 56, "video_tail": 48, "video_start": 4, "video_stop": 80}
     B.set_forward_context(SimpleNamespace(current_timestep=12, minimax_h3_layout=layout3))
-    assert B._h3_video_tokens_from_layout(used) == 48
-    video, (vid, ctx) = B._h3_cond_sparse_rows(used, torch.device("cpu"))
+    assert B._h3_split(used, "dense", cpu) == (48, None)
+    video, (vid, ctx) = B._h3_split(used, "sparse", cpu)
     assert video == 56 and vid.tolist() == list(range(4, 12)) + list(range(32, 80))
     assert ctx.tolist() == list(range(0, 4)) + list(range(12, 32))
     B.set_backend_config({"t2t_h3_cond_mode": "sparse", "t2t_cq": 4, "t2t_ck": 8})

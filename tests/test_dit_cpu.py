@@ -46,7 +46,8 @@ def _worker(rank, world, port, q):
         model = DiTStep(TINY, device="cpu", dtype=torch.float32, seed=7, make_attn=DenseStandIn,
                         group=dist.group.WORLD)
         out = model.forward(x[rank * n:(rank + 1) * n].contiguous(), text, 500.0, None)
-        q.put((rank, out))
+        # by value: a tensor would travel as a shared-memory handle that dies with this process
+        q.put((rank, out.numpy().copy()))
     finally:
         dist.destroy_process_group()
 
@@ -59,7 +60,7 @@ def test_sequence_sharded_step_equals_the_unsharded_step():
     assert (whole - x).abs().max() > 1e-3          # the step does something
     from conftest import run_gloo_ranks
     parts = dict(run_gloo_ranks(_worker, 2))
-    got = torch.cat([parts[0], parts[1]])
+    got = torch.cat([torch.from_numpy(parts[0]), torch.from_numpy(parts[1])])
     assert (got - whole).abs().max() <= 1e-4 * whole.abs().max()
 
 

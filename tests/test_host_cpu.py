@@ -56,8 +56,24 @@ def test_rebuild_reuse_schedule_matches_the_reference_rule():
 def test_unannotated_calls_always_rebuild_and_do_not_consume_annotations():
     op = _bare_operator(mask_refresh=4)
     assert _run_schedule(op, [(None, 0, 0), (None, 0, 0)]) == ["rebuild", "rebuild"]
-    assert op._cfg_hold == {}
     assert _run_schedule(op, [(0, 3, 0), (None, 0, 0), (1, 3, 0)]) == ["rebuild", "rebuild", "reuse"]
+
+
+def test_unannotated_rebuild_is_stored_under_the_last_annotation_like_the_reference():
+    """With snapshots switched on the reference stores every rebuild, also the one of a call without
+    set_cfg_call, under the key and step of the last annotation (deploy_step.py:420-440); a later
+    annotated branch-1 call of that key then reuses it."""
+    op = _bare_operator(mask_refresh=4)
+    assert _run_schedule(op, [(None, 0, 0)]) == ["rebuild"]
+    assert list(op._cfg_hold) == [0] and op._cfg_hold[0]["name"] == "fresh" and op._cfg_hold[0]["step"] == 0
+    assert _run_schedule(op, [(1, 0, 0)]) == ["reuse"]
+    first = op._cfg_hold[0]
+    assert _run_schedule(op, [(None, 0, 0)]) == ["rebuild"]
+    assert op._cfg_hold[0] is not first              # tensors of its own, the old snapshot is left alone
+    # snapshots off: nothing is stored and the shared structure is used
+    off = _bare_operator(mask_refresh=1)
+    assert _run_schedule(off, [(None, 0, 0), (0, 0, 0), (1, 0, 0)]) == ["rebuild"] * 3
+    assert off._cfg_hold == {}
 
 
 def test_step_counter_going_backwards_and_reset_force_a_rebuild():

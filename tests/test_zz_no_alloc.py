@@ -60,4 +60,23 @@ def test_static_scratch_variant_rejects_shapes_beyond_its_capacity(lib):
     rc = lib.t2t_vstats_gather_static(v.data_ptr(), kperm.data_ptr(), kcounts.data_ptr(), out[0].data_ptr(),
                                       out[1].data_ptr(), out[2].data_ptr(), H, N, C, st)
     assert rc == 4
+    # the second limit: at most 4 heads, whatever the cluster count (8 * 1024 = 8192 clusters would fit the first)
+    rc = lib.t2t_vstats_gather_static(v.data_ptr(), kperm.data_ptr(), kcounts.data_ptr(), out[0].data_ptr(),
+                                      out[1].data_ptr(), out[2].data_ptr(), 8, N, 1024, st)
+    assert rc == 4
     torch.cuda.synchronize()
+
+
+def test_static_scratch_variant_at_exactly_its_capacity(lib):
+    H, N, C = 4, 2048, 2048                                  # 4 heads x 2048 clusters: both limits met exactly
+    st = torch.cuda.current_stream().cuda_stream
+    ws = torch.empty(lib.t2t_vstats_gather_ws_bytes(H, C), dtype=torch.uint8, device=DEV)
+    v, kperm, kcounts = _inputs(H, N, C, 24)
+    want, got = _outputs(H, N, C), _outputs(H, N, C)
+    assert lib.t2t_vstats_gather(v.data_ptr(), kperm.data_ptr(), kcounts.data_ptr(), want[0].data_ptr(),
+                                 want[1].data_ptr(), want[2].data_ptr(), H, N, C, ws.data_ptr(), ws.numel(), st) == 0
+    assert lib.t2t_vstats_gather_static(v.data_ptr(), kperm.data_ptr(), kcounts.data_ptr(), got[0].data_ptr(),
+                                        got[1].data_ptr(), got[2].data_ptr(), H, N, C, st) == 0
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a.view(torch.int16) if a.dtype == BF else a, b.view(torch.int16) if b.dtype == BF else b)

@@ -628,7 +628,8 @@ extern "C" size_t t2t_vstats_gather_static_max_hc(void) { return T2T_STATIC_VSTA
 extern "C" int t2t_vstats_gather_static(const void* V, const void* kperm, const void* kcounts, void* V_sorted,
                                         void* sumv, void* lam, int H, int N, int C, cudaStream_t st) {
   if (!V || !kperm || !kcounts || !V_sorted || !sumv || !lam || H <= 0 || N <= 0 || C <= 0) return T2T_ERR_ARG;
-  if ((size_t)H * (size_t)C > (size_t)T2T_STATIC_VSTATS_MAX_HC) return T2T_ERR_TOO_LARGE;
+  // two limits: the per-cluster regions hold T2T_STATIC_VSTATS_MAX_HC clusters, the per-head one kStaticMaxHeads heads
+  if (H > kStaticMaxHeads || (size_t)H * (size_t)C > (size_t)T2T_STATIC_VSTATS_MAX_HC) return T2T_ERR_TOO_LARGE;
   VstatWs probe = vstat_layout(H, C, nullptr);
   if (probe.total > kStaticScratchBytes) return T2T_ERR_TOO_LARGE;
   int dev = -1;

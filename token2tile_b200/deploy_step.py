@@ -226,6 +226,9 @@ class MaskedStepDeploy:
         self.tailw_t = torch.tensor(float(tailw), device=dev, dtype=f32)
         self.ns_t = torch.tensor(self.ns, device=dev, dtype=i32)
         self.status = torch.zeros(1, device=dev, dtype=i32)
+        # host copy of the status word, refreshed asynchronously after every step() (see check_status)
+        self._status_host = torch.zeros(1, dtype=i32).pin_memory() if dev.type == "cuda" else torch.zeros(1, dtype=i32)
+        self._status_event = None
         L = self.lib
         self._tile_attn_plan_ints = int(L.t2t_tile_attn_plan_ints(H, N, CQ))
         ws = max(int(L.t2t_kmeans_maintain_ws_bytes(H, N, CQ, C)),
@@ -311,34 +314,42 @@ class MaskedStepDeploy:
         return newc, counts
 
     # -- state init ------------------------------------------------------------
+    def warm_start(self, q, k, Uq, Uk, rows_k, rows_q, warm_iters):
+        """Common tail of the state initialisers: rounds the fitted projections to
+        bfloat16, projects q and k, takes the rows `rows_k` / `rows_q` (sorted row
+        indices on the device) of the projected keys / queries as first centroids
+        and runs `warm_iters` Lloyd rounds on each side with the operator's exact
+        assignment and deterministic fixed-point mean.  Queues work on the current
+        stream of the operator's device; does not synchronise."""
+        with torch.cuda.device(self.dev):
+            st = _stream_ptr(torch.cuda.current_stream(self.dev))
+            state = {"Uq": Uq.to(BF16).contiguous(), "Uk": Uk.to(BF16).contiguous()}
+            labels = torch.empty(self.H, self.N, device=self.dev, dtype=torch.int32)
+            for side, x, proj, rows in (("ck", k, state["Uk"], rows_k), ("cq", q, state["Uq"], rows_q)):
+                low = torch.empty_like(self.KU)
+                self._project(x, proj, low, st)
+                cen = low[:, rows, :].contiguous()
+                for _ in range(warm_iters):
+                    self._assign(low, cen, labels, st)
+                    cen, _ = self._centroid_update(low, labels, cen, st)
+                state[side] = cen.contiguous()
+        return state
+
     def init_state(self, q, k, *, warm_iters=4, seed=0):
-        """Projections and initial centroids of one layer (deploy_step.py:245-266).
-        The projections are kept for the whole request; the centroids warm-start
-        every rebuild.  The warm Lloyd iterations use the exact assignment kernel
-        and the deterministic fixed-point centroid update."""
+        """Projections and first centroids of one layer (deploy_step.py:245-266):
+        the projection fit (`online_u`, raising on non-finite input), C key rows
+        and CQ query rows drawn by a seeded CPU generator as first centroids, and
+        `warm_iters` Lloyd rounds per side.  The projections stay for the whole
+        request; the centroids warm-start every rebuild.  Ends with a host
+        synchronisation, like the reference."""
         self._check_qkv(q, k)
-        N, r = self.N, self.r
-        Uq, Uk = online_u(q, k, r)
-        Uq = Uq.to(BF16).contiguous()
-        Uk = Uk.to(BF16).contiguous()
-        st = _stream_ptr(torch.cuda.current_stream(self.dev))
-        KU = torch.empty_like(self.KU)
-        QU = torch.empty_like(self.QU)
-        self._project(k, Uk, KU, st)
-        self._project(q, Uq, QU, st)
-        g = torch.Generator(device="cpu").manual_seed(seed)
-        ik = torch.randperm(N, generator=g)[: self.C].sort().values.to(self.dev)
-        iq = torch.randperm(N, generator=g)[: self.CQ].sort().values.to(self.dev)
-        ck = KU[:, ik, :].contiguous()
-        cq = QU[:, iq, :].contiguous()
-        lab = torch.empty(self.H, N, device=self.dev, dtype=torch.int32)
-        for _ in range(warm_iters):
-            self._assign(KU, ck, lab, st)
-            ck, _ = self._centroid_update(KU, lab, ck, st)
-            self._assign(QU, cq, lab, st)
-            cq, _ = self._centroid_update(QU, lab, cq, st)
+        Uq, Uk = online_u(q, k, self.r)
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        rows_k = torch.randperm(self.N, generator=gen)[: self.C].sort().values.to(self.dev)
+        rows_q = torch.randperm(self.N, generator=gen)[: self.CQ].sort().values.to(self.dev)
+        state = self.warm_start(q, k, Uq, Uk, rows_k, rows_q, warm_iters)
         torch.cuda.synchronize(self.dev)
-        return {"Uq": Uq, "Uk": Uk, "ck": ck.contiguous(), "cq": cq.contiguous()}
+        return state
 
     def set_cfg_call(self, parity, key=0, step=0):
         """Annotate the next step() call (deploy_step.py:268-277): parity is the
@@ -355,23 +366,31 @@ class MaskedStepDeploy:
         self._cfg_parity = None
 
     def _pick(self):
-        """Rebuild / reuse decision (deploy_step.py:297-316).  Returns
-        (snapshot to reuse or None, structure tensors a rebuild writes)."""
-        snap = None
-        held = None
-        parity = self._cfg_parity
-        self._cfg_parity = None          # an unannotated call never consumes a stale annotation
-        if self._cfg_on and parity is not None:
-            held = self._cfg_hold.get(self._cfg_key)
-            age = None if held is None else self._cfg_step - held["step"]
-            refresh_due = age is None or age < 0 or age >= self.mask_refresh
-            if held is not None and age >= 0 and not (parity == 0 and refresh_due):
-                snap = held
-            if snap is None:
-                # a rebuild overwrites the tensors of the snapshot it replaces
-                target = held if held is not None else self._new_structure()
-                return None, target, True
-        return snap, self._struct, False
+        """Decides between a rebuild and a reuse call (deploy_step.py:297-316, 420-440).
+        Returns (snapshot, structure, publish): the snapshot to reuse (None for a
+        rebuild), the set of structure tensors a rebuild writes into, and whether
+        the rebuilt structure becomes the stored snapshot of the current key.
+
+        An annotated call (set_cfg_call) looks its key up: the stored snapshot is
+        reused unless this is branch 0 and the snapshot is mask_refresh steps
+        old, or the step counter ran backwards (a new request).  Its rebuild
+        recycles the tensors of the snapshot it replaces.  An unannotated call
+        always rebuilds; with snapshots switched on the result is still stored,
+        under the key and step of the last annotation, in tensors of its own -
+        as the reference does, so a later annotated call of that key can reuse it."""
+        parity, self._cfg_parity = self._cfg_parity, None      # an annotation is good for one call
+        if not self._cfg_on:
+            return None, self._struct, False
+        if parity is None:
+            return None, self._new_structure(), True
+        stored = self._cfg_hold.get(self._cfg_key)
+        if stored is not None:
+            age = self._cfg_step - stored["step"]
+            stale = age >= self.mask_refresh
+            if age >= 0 and not (parity == 0 and stale):
+                return stored, self._struct, False
+            return None, stored, True
+        return None, self._new_structure(), True
 
     # -- the attention call ------------------------------------------------------
     def step(self, q, k, v, state, out=None):
@@ -383,6 +402,7 @@ class MaskedStepDeploy:
         still reads the previous result while the next call runs (a copy to the
         host in flight, say) alternates two `out` tensors."""
         self._check_qkv(q, k, v)
+        self.check_status(wait=False)
         if out is None:
             out = self.tile_attn_out
         elif (out.shape != self.tile_attn_out.shape or out.dtype != BF16 or out.device != self.tile_attn_out.device
@@ -454,6 +474,11 @@ class MaskedStepDeploy:
                 ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(out),
                 H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_merge")
             self._mark("residual_merge")
+            # the status word travels to pinned host memory behind the kernels; nobody waits for it here
+            self._status_host.copy_(self.status, non_blocking=True)
+            if self._status_event is None:
+                self._status_event = torch.cuda.Event()
+            self._status_event.record(self.s_main)
         self.last_rebuilt = snap is None
         self.last_structure = S
         # order the caller's stream after ours instead of a host sync
@@ -463,6 +488,28 @@ class MaskedStepDeploy:
         return out
 
     # -- diagnostics -------------------------------------------------------------
+    def check_status(self, wait=True):
+        """Raises RuntimeError if a kernel of an earlier step() reported that one of its
+        bounded waits gave up or that a task plan exceeded its bounds (the output of that
+        call is then unusable).  step() copies the device status word to pinned host
+        memory behind its kernels; with wait=False (what step() itself does on entry) only
+        a copy that has already arrived is looked at, so the hot path never synchronises;
+        with wait=True (request boundaries) the last copy is waited for."""
+        ev = self._status_event
+        if ev is None:
+            return
+        if wait:
+            ev.synchronize()
+        elif not ev.query():
+            return
+        code = int(self._status_host[0])
+        if code != 0:
+            self._status_host.zero_()
+            with torch.cuda.device(self.dev):
+                self.status.zero_()
+            raise RuntimeError(f"Token2Tile kernels reported status {code}: {_lib.STATUS.get(code, 'unknown')}; "
+                               "the result of the affected call is not valid")
+
     def device_status(self) -> int:
         """Status word of the bounded device waits (synchronises)."""
         return int(self.status.item())
@@ -470,8 +517,9 @@ class MaskedStepDeploy:
     def plan_info(self):
         """(tasks, executed query-key pairs) of the structure used last (synchronises)."""
         info = torch.zeros(4, device=self.dev, dtype=torch.int32)
-        st = _stream_ptr(torch.cuda.current_stream(self.dev))
-        check(self.lib.t2t_tile_attn_plan_info(ptr(self.last_structure["tile_attn_plan"]), self.H, self.N,
-                                               self.CQ, ptr(info), st), "t2t_tile_attn_plan_info")
+        with torch.cuda.device(self.dev):
+            st = _stream_ptr(torch.cuda.current_stream(self.dev))
+            check(self.lib.t2t_tile_attn_plan_info(ptr(self.last_structure["tile_attn_plan"]), self.H, self.N,
+                                                   self.CQ, ptr(info), st), "t2t_tile_attn_plan_info")
         a = info.cpu().tolist()
         return a[0], (a[1] & 0xFFFFFFFF) | ((a[2] & 0xFFFFFFFF) << 32)

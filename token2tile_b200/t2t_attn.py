@@ -547,6 +547,14 @@ def _order_after_caller(deploy, device) -> None:
         deploy.s_side.wait_stream(current)
 
 
+def _check_operator_status(deploy) -> None:
+    """Waits for and examines the operator's device status word (an operator without the
+    method - a stand-in, the reference's own class - is left alone)."""
+    check = getattr(deploy, "check_status", None)
+    if check is not None:
+        check(wait=True)
+
+
 def _set_budget(deploy, ns_tensor, device) -> None:
     """ns_t <- budget, ordered on the operator's main stream (t2t_attn.py:1176-1177)."""
     if device.type == "cuda":
@@ -572,31 +580,24 @@ def fast_online_u(qf, kf, r: int = 32):
 
 
 def make_fast_init_state(deploy, module=None):
-    """Replacement for `MaskedStepDeploy.init_state` (t2t_attn.py:260-281):
-    fp32-moment projection fit, centroid rows sampled by a device generator,
-    no trailing host synchronisation.  The Lloyd iterations are the operator's
-    own assignment kernel and deterministic fixed-point centroid update."""
+    """`t2t_fast_init`: an `init_state` for `deploy` that never touches the host
+    (the role of the reference's replacement, t2t_attn.py:260-281): projection
+    fit without the finiteness read-back, first centroids drawn by a generator
+    on the device, no trailing synchronisation.  Everything after the draw is
+    the operator's own `warm_start`, so the Lloyd rounds are the same kernels
+    as in `MaskedStepDeploy.init_state`."""
 
     def init_state(q, k, *, warm_iters=4, seed=0):
-        N, r = deploy.N, deploy.r
-        Uq, Uk = fast_online_u(q, k, r)
-        Uq = Uq.to(KERNEL_DTYPE).contiguous()
-        Uk = Uk.to(KERNEL_DTYPE).contiguous()
-        st = torch.cuda.current_stream(deploy.dev).cuda_stream
-        KU = torch.empty_like(deploy.KU)
-        QU = torch.empty_like(deploy.QU)
-        deploy._project(k, Uk, KU, st)
-        deploy._project(q, Uq, QU, st)
-        g = torch.Generator(device=q.device).manual_seed(seed)
-        ck = KU[:, torch.randperm(N, generator=g, device=q.device)[: deploy.C].sort().values, :].contiguous()
-        cq = QU[:, torch.randperm(N, generator=g, device=q.device)[: deploy.CQ].sort().values, :].contiguous()
-        lab = torch.empty(deploy.H, N, device=q.device, dtype=torch.int32)
-        for _ in range(warm_iters):
-            deploy._assign(KU, ck, lab, st)
-            ck, _ = deploy._centroid_update(KU, lab, ck, st)
-            deploy._assign(QU, cq, lab, st)
-            cq, _ = deploy._centroid_update(QU, lab, cq, st)
-        return {"Uq": Uq, "Uk": Uk, "ck": ck.contiguous(), "cq": cq.contiguous()}
+        with torch.cuda.device(deploy.dev):
+            Uq, Uk = fast_online_u(q, k, deploy.r)
+            gen = torch.Generator(device=deploy.dev).manual_seed(seed)
+
+            def draw(count):
+                return torch.randperm(deploy.N, generator=gen, device=deploy.dev)[:count].sort().values
+
+            rows_k = draw(deploy.C)
+            rows_q = draw(deploy.CQ)
+            return deploy.warm_start(q, k, Uq, Uk, rows_k, rows_q, warm_iters)
 
     return init_state
 
@@ -658,38 +659,37 @@ def _h3_layout():
     return getattr(context, "minimax_h3_layout", None) if context is not None else None
 
 
-def _h3_video_tokens_from_layout(used_tokens: int) -> int:
-    """Length of the sparse video tail of the packed document, from the layout
-    the model publishes on the forward context; 0 when this call is not the
-    main packed document or the video segment is not its contiguous tail
-    (t2t_attn.py:869-889)."""
+def _h3_split(used_tokens: int, cond_mode: str, device):
+    """Where the sparse video rows of a packed document of `used_tokens` rows lie,
+    from the layout the model publishes on the forward context
+    (t2t_attn.py:869-908).  Returns (video_tokens, rows): video_tokens = 0 when
+    this call is not the main packed document (then it stays dense); rows =
+    None when the video rows are simply the tail of the document, else a pair
+    (video row ids, context row ids) - the "sparse" condition mode, where the
+    video rows are [condition rows | generated tail] and everything else is
+    context."""
     layout = _h3_layout()
-    if not layout or layout["video"] <= 0:
-        return 0
-    video = int(layout["video"])
+    if not layout:
+        return 0, None
+    video = int(layout.get("video", 0))
+    stop_ok = layout.get("video_stop") == used_tokens
+    if cond_mode == "sparse" and "video_tail" in layout and stop_ok:
+        tail = int(layout["video_tail"])
+        cond = video - tail
+        if cond > 0:
+            first = int(layout["video_start"])
+            ids = torch.arange(used_tokens)
+            is_video = ((ids >= first) & (ids < first + cond)) | (ids >= used_tokens - tail)
+            return video, (ids[is_video].to(device), ids[~is_video].to(device))
+    if video <= 0 or not stop_ok:
+        return 0, None
     tail = int(layout.get("video_tail", video))
-    if layout["video_stop"] != used_tokens or tail <= 0:
-        return 0
-    if layout["video_start"] != used_tokens - video and tail == video:
-        return 0
-    return tail
-
-
-def _h3_cond_sparse_rows(used_tokens: int, device):
-    """cond_mode "sparse": (video token count, (video row ids, context row
-    ids)) with the video rows = [condition rows | generated tail]; None when the
-    document has no condition rows (t2t_attn.py:892-908)."""
-    layout = _h3_layout()
-    if not layout or "video_tail" not in layout:
-        return None
-    video, tail = int(layout["video"]), int(layout["video_tail"])
-    cond = video - tail
-    if cond <= 0 or layout["video_stop"] != used_tokens:
-        return None
-    c0 = int(layout["video_start"])
-    vid = torch.cat((torch.arange(c0, c0 + cond), torch.arange(used_tokens - tail, used_tokens)))
-    ctx = torch.cat((torch.arange(0, c0), torch.arange(c0 + cond, used_tokens - tail)))
-    return video, (vid.to(device), ctx.to(device))
+    if tail <= 0:
+        return 0, None
+    # without condition rows the video segment has to be the contiguous tail of the document
+    if tail == video and layout["video_start"] != used_tokens - video:
+        return 0, None
+    return tail, None
 
 
 def h3_auto_cq(used_tokens: int) -> int:
@@ -769,29 +769,29 @@ class T2TAttentionImpl(AttentionImpl):
 
     def __init__(self, num_heads: int, head_size: int, causal: bool, softmax_scale: float,
                  num_kv_heads: int | None = None, prefix: str = "", **extra_impl_args: Any) -> None:
-        if causal:
-            raise ValueError("Token2Tile does not support causal attention")
-        if head_size != 128:
-            raise ValueError("Token2Tile kernels require head dimension 128")
-        if num_kv_heads not in (None, num_heads):
-            raise ValueError("Token2Tile does not support grouped-query attention")
-        if not math.isclose(softmax_scale, 1.0 / math.sqrt(128), rel_tol=1e-6):
-            raise ValueError("Token2Tile has a fixed 1/sqrt(128) attention scale")
-        self.num_heads = num_heads
-        self.head_size = head_size
-        self.softmax_scale = softmax_scale
+        unsupported = (
+            (bool(causal), "Token2Tile does not support causal attention"),
+            (head_size != 128, "Token2Tile kernels require head dimension 128"),
+            (num_kv_heads is not None and num_kv_heads != num_heads, "Token2Tile does not support grouped-query attention"),
+            (not math.isclose(softmax_scale, 128 ** -0.5, rel_tol=1e-6), "Token2Tile has a fixed 1/sqrt(128) attention scale"),
+        )
+        for hit, message in unsupported:
+            if hit:
+                raise ValueError(message)
+        self.num_heads, self.head_size, self.softmax_scale = num_heads, head_size, softmax_scale
         self.layer_idx = self._get_layer_idx(prefix)
         self._h3_states: dict[int, dict[str, torch.Tensor]] = {}
         self._dense = DenseAttention(num_heads, head_size, softmax_scale, num_kv_heads, prefix)
 
     @staticmethod
     def _get_layer_idx(prefix: str) -> int:
-        """Layer index from the module path: "...blocks.<i>..." or, failing
-        that, the third component from the end (t2t_attn.py:1082-1090)."""
-        match = re.search(r"(?:blocks|transformer_blocks)\.(\d+)", prefix)
-        if match is not None:
-            return int(match.group(1))
+        """Index of the transformer block a module path belongs to
+        (t2t_attn.py:1082-1090): the number after a "blocks" / "transformer_blocks"
+        component, else the third component from the end."""
         parts = prefix.split(".")
+        for name, nxt in zip(parts, parts[1:]):
+            if name in ("blocks", "transformer_blocks") and nxt.isdigit():
+                return int(nxt)
         if len(parts) < 3:
             raise ValueError(f"Invalid Token2Tile attention layer prefix: {prefix}")
         return int(parts[-3])
@@ -826,6 +826,9 @@ class T2TAttentionImpl(AttentionImpl):
         elif cache.runtime_key != runtime.key:
             raise RuntimeError("Token2Tile request geometry changed during denoising")
         if runtime.active_cache_id != id(cache):       # a new request: its snapshots start empty
+            # the request boundary is also where the device status word of the previous request's calls is
+            # examined: a kernel whose bounded wait gave up leaves garbage behind, and step() itself never syncs
+            _check_operator_status(runtime.deploy)
             runtime.deploy.reset_cfg_reuse()
             runtime.active_cache_id = id(cache)
             cache.initialized_runtime = True
@@ -884,14 +887,12 @@ class T2TAttentionImpl(AttentionImpl):
             raise ValueError(f"Invalid H3 packed used length {used}/{query.shape[0]}")
         # The same backend also serves short auxiliary sequences (the prompt
         # refiner): anything that is not the main packed document stays dense.
-        video_tokens = cfg["video_tokens"]
-        if video_tokens <= 0:
-            video_tokens = _h3_video_tokens_from_layout(used)
-        rows = None
-        if cfg["cond_mode"] == "sparse":
-            sparse = _h3_cond_sparse_rows(used, query.device)
-            if sparse is not None:
-                video_tokens, rows = sparse
+        video_tokens, rows = cfg["video_tokens"], None
+        from_layout, layout_rows = _h3_split(used, cfg["cond_mode"], query.device)
+        if layout_rows is not None:
+            video_tokens, rows = from_layout, layout_rows
+        elif video_tokens <= 0:
+            video_tokens = from_layout
         if video_tokens <= 0 or video_tokens >= used:
             return dense()
         local_heads = int(query.shape[1])
@@ -914,6 +915,7 @@ class T2TAttentionImpl(AttentionImpl):
             else:
                 self._h3_states.clear()
             if self.layer_idx == 0:
+                _check_operator_status(deploy)      # the previous request's calls: see forward()
                 deploy.reset_cfg_reuse()
 
         device = query.device
