@@ -448,6 +448,7 @@ def run_ours(args, rank, world, local_rank):
     except Exception as exc:      # noqa: BLE001
         print(f"[bench] init timing skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
 
+    ns_layer = op.ns
     # BASELINE configuration 2: the 480p layer (32,760 tokens, 256 query clusters), budgets 1.5 % and 5 %
     config2 = None
     if not (args.heads or args.grid):
@@ -457,6 +458,26 @@ def run_ours(args, rank, world, local_rank):
             config2 = layer_480p(dev, lo, hi, maxr, barrier)
         except Exception as exc:      # noqa: BLE001 - a second, informative measurement
             print(f"[bench] 480p configuration skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
+
+    # BASELINE configuration 5 at eight GPUs: the full transformer step (40 blocks, Ulysses x8) with Token2Tile
+    # and with dense self-attention, one refresh period each
+    dit = None
+    if world == 8 and not (args.heads or args.grid):
+        try:
+            del op, opr, state, state0
+            torch.cuda.empty_cache()
+            dit = {}
+            for name, dense_attn in (("token2tile", False), ("dense", True)):
+                rec = dit_measure(rank, world, dev, dist.group.WORLD, dense_attention=dense_attn, steps=4, warmup=4,
+                                  with_e2e=False)
+                if rec is not None:
+                    dit[name] = {"ms_per_step": rec["value"], "config": rec["config"], "clocks": rec["clocks"],
+                                 "gemm_TFLOPs": rec["roofline"]["achieved"], "gpu_launches": rec["gpu_launches"]}
+            if rank == 0 and "dense" in dit and "token2tile" in dit:
+                dit["speedup_vs_dense_attention"] = dit["dense"]["ms_per_step"] / dit["token2tile"]["ms_per_step"]
+        except Exception as exc:      # noqa: BLE001 - the headline metric does not depend on it
+            print(f"[bench] transformer step skipped: {type(exc).__name__}: {exc}", file=sys.stderr)
+            dit = None
 
     pk = peaks()
     flops = 4.0 * W["D"] * pairs
@@ -532,7 +553,7 @@ def run_ours(args, rank, world, local_rank):
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": W["name"], "H": W["H"], "heads_per_gpu": Hl, "N": N, "CQ": CQ, "D": W["D"],
-                       "budget": W["s_frac"], "ns": op.ns, "call": "rebuild (mask_refresh=1)",
+                       "budget": W["s_frac"], "ns": ns_layer, "call": "rebuild (mask_refresh=1)",
                        "parallelism": f"head-parallel x{world}", "l2": "inputs (2.3 GB/step) exceed L2; no flush"},
             "roofline": roofline, "cpu_baseline": cpu,
             "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": bytes_in,
@@ -544,7 +565,7 @@ def run_ours(args, rank, world, local_rank):
             "reuse_ms": reuse_ms, "amortised_ms_1_rebuild_7_reuse": amort, "stages_ms": stages,
             "reuse_stages_ms": reuse_stages, "stage_roofline": stage_roof, "tasks": tasks,
             "dense_ms": dense, "fastest_dense_ms": dense_best, "budgets": budgets, "init_ms": init_ms,
-            "config_480p": config2,
+            "config_480p": config2, "dit_step_ulysses8": dit,
             "speedup_vs_dense": {"rebuild": dense_best / ms_step, "reuse": dense_best / reuse_ms,
                                  "amortised": dense_best / amort} if dense_best else None,
         }
@@ -557,24 +578,21 @@ def run_ours(args, rank, world, local_rank):
 # full transformer step (40 blocks, Ulysses sequence parallelism at N > 1)
 # ---------------------------------------------------------------------------
 
-def run_dit(args, rank, world, local_rank):
-    """One denoising step = both CFG branches through all blocks.  The timed
-    steps cover one refresh period of the structure (mask_refresh = 4): the
-    first rebuilds in branch 0, everything else reuses."""
+def dit_measure(rank, world, dev, group, *, grid_name="720p", blocks=0, dense_attention=False, steps=4, warmup=4,
+                with_e2e=True):
+    """One denoising step = both CFG branches through all blocks.  The timed steps cover whole refresh periods
+    of the structure (mask_refresh = 4): the first step of a period rebuilds in branch 0, everything else
+    reuses.  Returns the bench record of the workload (rank 0) or None; the process group, if any, is the
+    caller's."""
     import torch.distributed as dist
     from token2tile_b200 import dit_step as D
     from token2tile_b200 import t2t_attn as B
     from token2tile_b200.synth import GRIDS
 
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
-    group = None
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-        group = dist.group.WORLD
-        B.set_ulysses_world_size(world)
+    B.clear_runtimes()
+    B.set_ulysses_world_size(world)
     shape = D.WAN_14B
-    grid = GRIDS[args.grid or "720p"]
+    grid = GRIDS[grid_name]
     N = grid[0] * grid[1] * grid[2]
     CQ = {75600: 512, 32760: 256}.get(N, max(32, N // 128))
     ns = max(1, int(0.015 * N))
@@ -589,9 +607,9 @@ def run_dit(args, rank, world, local_rank):
         def forward(self, q, k, v, meta):
             return self.dense.forward(q, k, v)
 
-    nblocks = args.blocks or shape.blocks
+    nblocks = blocks or shape.blocks
     model = D.DiTStep(shape, device=dev, seed=0, group=group, blocks=nblocks,
-                      make_attn=DenseImpl if args.dense_attention else None)
+                      make_attn=DenseImpl if dense_attention else None)
     # residual stream: a locality mixture in the model width (512 centres, blocks of 1x4x4 tokens)
     g = torch.Generator(device=dev).manual_seed(1234)
     T, Y, X = grid
@@ -645,26 +663,28 @@ def run_dit(args, rank, world, local_rank):
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
         return float(tt.item())
 
-    warm = max(4, (args.warmup + 3) // 4 * 4)       # whole refresh periods, so the timed steps start with a rebuild
+    warm = max(4, (warmup + 3) // 4 * 4)       # whole refresh periods, so the timed steps start with a rebuild
     for _ in range(warm):
         denoise_step()
     barrier()
-    steps = args.steps
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(dev.index or 0) if rank == 0 else None
     rebuilds = sum(1 for s_ in range(counter[0], counter[0] + steps) if s_ % 4 == 0)   # branch-0 calls that rebuild
     ms = time_events(denoise_step, steps)
     barrier()
     clocks = sampler.stop() if sampler else None
     ms_step = maxr(ms / steps)
-    counter[0] = (counter[0] + 3) // 4 * 4
-    denoise_step(host=True)
-    barrier()
-    counter[0] = (counter[0] + 3) // 4 * 4
-    e2e_ms = maxr(time_events(lambda: denoise_step(host=True), steps) / steps)
-    barrier()
-    if not args.dense_attention:
+    e2e_ms = None
+    if with_e2e:
+        counter[0] = (counter[0] + 3) // 4 * 4
+        denoise_step(host=True)
+        barrier()
+        counter[0] = (counter[0] + 3) // 4 * 4
+        e2e_ms = maxr(time_events(lambda: denoise_step(host=True), steps) / steps)
+        barrier()
+    if not dense_attention:
         for rt in B._RUNTIMES.values():
             assert rt.deploy.device_status() == 0, "a device wait timed out"
+    line = None
     if rank == 0:
         pk = peaks()
         gemm_flops = 2 * D.flops_per_step(D.DiTShape(blocks=nblocks), N) / world      # two branches, this rank's tokens
@@ -672,9 +692,9 @@ def run_dit(args, rank, world, local_rank):
             "metric": "dit_denoising_step_ms", "value": ms_step, "unit": "ms/step", "n_gpus": world, "steps": steps,
             "warmup": warm, "ms_per_step": ms_step, "higher_is_better": False, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "wan2.1-14b-shaped-dit-step-" + (args.grid or "720p"), "blocks": nblocks,
+            "config": {"workload": "wan2.1-14b-shaped-dit-step-" + grid_name, "blocks": nblocks,
                        "dim": shape.dim, "heads": shape.heads, "ffn": shape.ffn, "N": N, "text_tokens": shape.text_len,
-                       "cfg_branches_per_step": 2, "rebuild_steps_in_timed_region": rebuilds, "self_attention": "dense" if args.dense_attention else
+                       "cfg_branches_per_step": 2, "rebuild_steps_in_timed_region": rebuilds, "self_attention": "dense" if dense_attention else
                        f"token2tile ns={ns} CQ={CQ} mask_refresh=4 cfg_reuse", "parallelism": f"ulysses x{world}",
                        "weights_GB": model.weight_bytes() / 1e9,
                        "all_to_all_bytes_per_rank_per_block": D.all_to_all_bytes_per_block(shape, N, world),
@@ -685,11 +705,28 @@ def run_dit(args, rank, world, local_rank):
                          "note": "GEMM FLOPs only over the whole step time: a lower bound on utilisation"},
             "cpu_baseline": None,
             "e2e": {"value": e2e_ms, "unit": "ms/step", "h2d_bytes_per_step": hx.numel() * 2,
-                    "d2h_bytes_per_step": hout.numel() * 2},
-            "gpu_launches": None if args.dense_attention else
+                    "d2h_bytes_per_step": hout.numel() * 2} if with_e2e else None,
+            "gpu_launches": None if dense_attention else
             nblocks * (rebuilds * KERNELS_REBUILD + (2 * steps - rebuilds) * KERNELS_REUSE),
             "clocks": clocks,
         }
+    del model, x_dev, hx, hout
+    B.clear_runtimes()
+    torch.cuda.empty_cache()
+    return line
+
+
+def run_dit(args, rank, world, local_rank):
+    import torch.distributed as dist
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    line = dit_measure(rank, world, dev, group, grid_name=args.grid or "720p", blocks=args.blocks,
+                       dense_attention=args.dense_attention, steps=args.steps, warmup=args.warmup)
+    if rank == 0:
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
