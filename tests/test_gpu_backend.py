@@ -40,6 +40,11 @@ def _wan_inputs(H=12):
     return tuple(t.transpose(0, 1).unsqueeze(0).contiguous().to(DEV) for t in (q, k, v))
 
 
+def cache_state_uq(impl):
+    """Query projection of the packed path's last head chunk (the implementation keeps one state per chunk)."""
+    return impl._h3_states[max(impl._h3_states)]["Uq"].cpu()
+
+
 def _meta(B, cache, step, **kw):
     return B.T2TAttentionMetadataBuilder().build(
         step, 50, cache, profile_name="manual", ns_base=204, dense_prefix_steps=1, cq=32, ck=2048,
@@ -107,6 +112,42 @@ def test_fast_init_state(backend):
     assert rel < 0.05, rel
 
 
+def test_fast_init_state_against_the_oracle(backend):
+    """`t2t_fast_init` end to end: the projections against the oracle's fit (as products Uq Uk^T), and the
+    first centroids bit for bit against the oracle's Lloyd rounds replayed from the device's own projected rows
+    and the same row draws (a device generator with the same seed repeats its draws)."""
+    B = backend
+    from oracle import t2t_oracle as O
+    from token2tile_b200 import MaskedStepDeploy
+    from token2tile_b200.synth import GRIDS, locality_mixture
+    H, N, CQ, warm, seed = 3, 4096, 32, 2, 5
+    q, k, _ = locality_mixture(H, GRIDS["cpu"])
+    qd, kd = q.to(DEV), k.to(DEV)
+    op = MaskedStepDeploy(H, N, CQ, s_frac=0.05)
+    st = B.make_fast_init_state(op)(qd, kd, warm_iters=warm, seed=seed)
+    torch.cuda.synchronize()
+    assert op.device_status() == 0
+    oq, ok = O.online_u(q.float(), k.float(), 32)
+    want = oq.to(BF).double() @ ok.to(BF).double().transpose(1, 2)
+    got = st["Uq"].cpu().double() @ st["Uk"].cpu().double().transpose(1, 2)
+    assert (got - want).abs().max() <= 0.02 * want.abs().max()
+    KU, QU = torch.empty_like(op.KU), torch.empty_like(op.QU)
+    stream = torch.cuda.current_stream().cuda_stream
+    op._project(kd, st["Uk"], KU, stream)
+    op._project(qd, st["Uq"], QU, stream)
+    gen = torch.Generator(device=DEV).manual_seed(seed)
+    rows_k = torch.randperm(N, generator=gen, device=DEV)[:2048].sort().values.cpu()
+    rows_q = torch.randperm(N, generator=gen, device=DEV)[:CQ].sort().values.cpu()
+    torch.cuda.synchronize()
+    KU, QU = KU.cpu(), QU.cpu()
+    ck, cq = KU[:, rows_k, :].contiguous(), QU[:, rows_q, :].contiguous()
+    for _ in range(warm):
+        ck, _ = O.fixed_point_mean(KU, O.assign(KU, ck), ck, BF)
+        cq, _ = O.fixed_point_mean(QU, O.assign(QU, cq), cq, BF)
+    assert torch.equal(st["ck"].cpu().view(torch.int16), ck.view(torch.int16))
+    assert torch.equal(st["cq"].cpu().view(torch.int16), cq.view(torch.int16))
+
+
 def test_packed_document_path(backend):
     B = backend
     from token2tile_b200.synth import locality_mixture
@@ -140,3 +181,29 @@ def test_packed_document_path(backend):
     rel = ((out[context:used].float() - dense[context:]).norm() / dense[context:].norm()).item()
     assert rel < 0.08, rel
     assert bool((out[used:] == 0).all())
+
+    # The operator's last call (heads 28..55) against the oracle.  Its rows are [video | context] for keys and
+    # values and [video | the first `context` video queries again] for the queries; the stages that follow the
+    # clustering are replayed from the device's own labels and projections: selection with the pinned context
+    # cluster bit for bit, exact attention + residual merge within the operator's tolerance.
+    from oracle import t2t_oracle as O
+    hs = slice(28, 56)
+    tok = lambda t, rows: t[rows, hs].transpose(0, 1).cpu()                      # [28, rows, 128]
+    vid, ctx = slice(context, used), slice(0, context)
+    q_op = torch.cat((tok(q, vid), tok(q, vid)[:, :context]), dim=1)
+    k_op = torch.cat((tok(k, vid), tok(k, ctx)), dim=1)
+    v_op = torch.cat((tok(v, vid), tok(v, ctx)), dim=1)
+    QU, cks, counts = dep.QU.cpu(), S["cks"].cpu(), S["counts"].cpu()
+    qlab, klab = S["qlab"].cpu(), S["klab"].cpu()
+    kcounts, kperm = O.stable_group(klab, 2048)
+    assert torch.equal(counts, kcounts) and torch.equal(S["kperm"].cpu(), kperm)
+    want_QU = O.project(q_op, cache_state_uq(impl), BF).float()
+    assert (QU.float() - want_QU).abs().max() <= want_QU.abs().max() * 2.0 ** -7
+    unip, rowcnt = O.select_union(QU, cks, counts, qlab, dep.CQ, int(dep.ns_t.item()), pin_tail=context)
+    assert torch.equal(S["unip"].cpu(), unip) and torch.equal(dep.rowcnt.cpu(), rowcnt)
+    _, sumv, lam, _ = O.vstats(v_op, kperm, kcounts, BF)
+    assert torch.equal(dep._kmm_sumv.cpu().view(torch.int16), sumv.view(torch.int16))
+    o, lse = O.exact_attention(q_op, k_op, v_op, qlab, klab, unip, SCALE)
+    want = O.residual_merge(o, lse, QU, cks, sumv, lam, counts, unip, qlab, 1.0)
+    err = (dep.tile_attn_out.float().cpu() - want).abs()
+    assert err.max() < 2e-2 and err.mean() < 2e-3, (float(err.max()), float(err.mean()))

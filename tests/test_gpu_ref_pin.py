@@ -82,8 +82,24 @@ def test_oracle_clustering_matches_reference_kernels(ref, case16, pin_tail):
             da = d.gather(1, r["klab"][h, rows].long()[:, None])
             db = d.gather(1, want["klab"][h, rows].long()[:, None])
             assert float(((da - db).abs() / db.abs().clamp_min(1.0)).max()) < 1e-4
-    qdiff = (r["qlab"] != want["qlab"]).float().mean()
-    assert qdiff < 2e-2, float(qdiff)
+    # Query labels come out of two passes.  The reference keeps the centroids between the passes (cq1) inside
+    # its workspace, so its second pass cannot be replayed from its own cq1; instead every disagreement must be
+    # a near-tie under the oracle's cq1.  A first-pass near-tie that goes the other way moves two centroids by
+    # about one row in a few hundred, i.e. by a few float16 ulps (2^-11 relative), and a distance is linear in
+    # the centroid: the two candidate distances of a disagreeing row may differ by that much, not by more.
+    qd = (r["qlab"] != want["qlab"])
+    qdiff = float(qd.float().mean())
+    worst = 0.0
+    for h in range(H):
+        rows = qd[h].nonzero().flatten()
+        if rows.numel():
+            cen = want["cq1"][h].float()
+            d = O.chain_dot(c["QU"][h, rows].float(), -2.0 * cen, O.centroid_norms(cen))
+            da = d.gather(1, r["qlab"][h, rows].long()[:, None])
+            db = d.gather(1, want["qlab"][h, rows].long()[:, None])
+            worst = max(worst, float(((da - db).abs() / db.abs().clamp_min(1.0)).max()))
+    print(f"query labels: {qdiff:.2e} of the rows differ, largest relative distance gap {worst:.2e}")
+    assert qdiff < 2e-3 and worst < 2e-2, (qdiff, worst)      # measured on a B200: no row differs on this case
 
     # everything downstream, with the reference's labels fed to the oracle
     kcounts, kperm = O.stable_group(r["klab"], 2048)

@@ -39,6 +39,7 @@ constexpr int ST_CAP = 64;                 // candidates per row
 constexpr int ST_REFINE = 40;              // refine the bucket when it alone holds more clusters than this
 constexpr int ST_MAX_ITERS = 5;
 constexpr int kMomFloats = 32 + 32 * 32;   // per head: mean centroid, second-moment matrix
+constexpr int kMomParts = 8;               // the moments are summed over this many slices of the centroids
 constexpr int ST_TPC = 4;                  // consecutive 128-row tiles of one head per CTA: the head's centroids, sizes
                                            // and prefix sums are staged once for all of them
 constexpr int ST_STRAGGLERS = 8;           // this few unsettled rows of a tile go to the exact kernel instead of another pass
@@ -132,7 +133,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
   cp_async_commit();
   for (int c = tid; c < kC; c += ST_THREADS) sSizeP[c] = (kcounts[(size_t)h * kC + c] << 12) + 1;
   float* sMom = reinterpret_cast<float*>(sm + OFF_MOM);
-  for (int i = tid; i < kMomFloats; i += ST_THREADS) sMom[i] = mom[(size_t)h * kMomFloats + i];
+  for (int i = tid; i < kMomFloats; i += ST_THREADS) {      // slices added in a fixed order
+    float acc = 0.f;
+#pragma unroll
+    for (int p = 0; p < kMomParts; ++p) acc += mom[((size_t)h * kMomParts + p) * kMomFloats + i];
+    sMom[i] = acc;
+  }
   __syncthreads();
   {
     // exclusive prefix sums of the query-cluster sizes
@@ -644,26 +650,30 @@ __global__ void pin_bit_kernel(int* __restrict__ unip, int rows) {
   if (i < rows) atomicOr(reinterpret_cast<unsigned*>(unip) + (size_t)i * 64 + 63, 0x80000000u);
 }
 
-// First two moments of a head's scaled key centroids: mom[h] = { mean_c c (32), mean_c c c^T (32 x 32) }.
+// First two moments of a head's scaled key centroids, as kMomParts partial sums (one CTA per slice of
+// C / kMomParts centroids): mom[h][p] = { sum_c c / C (32), sum_c c c^T / C (32 x 32) } over the slice.
 __global__ void __launch_bounds__(1024) centroid_moments_kernel(const __nv_bfloat16* __restrict__ cks,
                                                                 float* __restrict__ mom) {
-  const int h = blockIdx.x, a = threadIdx.x >> 5, b = threadIdx.x & 31;
-  const __nv_bfloat16* ch = cks + (size_t)h * kC * kR;
+  constexpr int SLICE = kC / kMomParts;
+  __shared__ float sc[SLICE][kR + 1];
+  const int h = blockIdx.y, part = blockIdx.x, a = threadIdx.x >> 5, b = threadIdx.x & 31;
+  const __nv_bfloat16* ch = cks + ((size_t)h * kC + (size_t)part * SLICE) * kR;
+  for (int i = threadIdx.x; i < SLICE * kR; i += 1024) sc[i >> 5][i & 31] = bf_to_f(ch[i]);      // coalesced
+  __syncthreads();
   float g0 = 0.f, g1 = 0.f, m0 = 0.f;
-  for (int c = 0; c < kC; c += 2) {
-    const float xa0 = bf_to_f(ch[c * kR + a]), xb0 = bf_to_f(ch[c * kR + b]);
-    const float xa1 = bf_to_f(ch[(c + 1) * kR + a]), xb1 = bf_to_f(ch[(c + 1) * kR + b]);
-    g0 = fmaf(xa0, xb0, g0);
-    g1 = fmaf(xa1, xb1, g1);
-    m0 += xb0 + xb1;
+#pragma unroll 4
+  for (int c = 0; c < SLICE; c += 2) {
+    g0 = fmaf(sc[c][a], sc[c][b], g0);
+    g1 = fmaf(sc[c + 1][a], sc[c + 1][b], g1);
+    m0 += sc[c][b] + sc[c + 1][b];
   }
-  float* mh = mom + (size_t)h * kMomFloats;
+  float* mh = mom + ((size_t)h * kMomParts + part) * kMomFloats;
   mh[32 + a * 32 + b] = (g0 + g1) * (1.0f / kC);
   if (a == 0) mh[b] = m0 * (1.0f / kC);
 }
 
 static size_t select_queue_bytes(int H, int N) { return ((size_t)H * (2 * (size_t)N + 1) * sizeof(int) + 255) & ~(size_t)255; }
-size_t select_ws_bytes(int H, int N) { return select_queue_bytes(H, N) + (size_t)H * kMomFloats * sizeof(float); }
+size_t select_ws_bytes(int H, int N) { return select_queue_bytes(H, N) + (size_t)H * kMomParts * kMomFloats * sizeof(float); }
 
 }  // namespace t2t
 
@@ -683,7 +693,7 @@ extern "C" int t2t_score_select_union(const void* QU, const void* cks, const voi
                                         st);
   int* fixq = (int*)ws;
   float* mom = reinterpret_cast<float*>((char*)ws + select_queue_bytes(H, N));
-  centroid_moments_kernel<<<H, 1024, 0, st>>>((const __nv_bfloat16*)cks, mom);
+  centroid_moments_kernel<<<dim3(kMomParts, H), 1024, 0, st>>>((const __nv_bfloat16*)cks, mom);
   if (cudaMemsetAsync(fixq, 0, select_queue_bytes(H, N), st) != cudaSuccess ||
       cudaMemsetAsync(unip, 0, (size_t)H * CQ * 64 * sizeof(int), st) != cudaSuccess)
     return T2T_ERR_CUDA;
