@@ -202,6 +202,38 @@ int t2t_tile_attn_merge(const void* QU, const void* cks, const void* sumv, const
  * Device-side; copies 4 ints into d_info. */
 int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, int* d_info, cudaStream_t stream);
 
+/* The same entry points for q, k, v (and the output) given as VIEWS of a tensor laid out [N, H, 128], the way
+ * the reference's serving host holds them (integrations/sglang/backend/t2t_attn.py:1160-1163, where the
+ * reference pays three transposing copies in and one out).  Row (h, n) of such a tensor starts at
+ * base + h * head_stride + n * row_stride (strides in ELEMENTS; 128 and N * 128 for the contiguous [H, N, 128]
+ * layout; 128 * H and 128 for a [N, H, 128] tensor).  Both strides must be multiples of 128 where a tensor
+ * feeds a TMA row gather (q of the attention, out of the merge) and of 8 elsewhere; the 128 elements of a row
+ * are contiguous.  Everything else is as in the entry points without the suffix, which forward here. */
+int t2t_project_strided(const void* x, long long x_row_stride, long long x_head_stride, const void* U, void* out,
+                        int H, int N, int* d_status, cudaStream_t stream);
+int t2t_lowrank_fit_strided(const void* q, const void* k, long long row_stride, long long head_stride, float* Uq,
+                            float* Uk, int H, int N, void* ws, size_t ws_bytes, int* d_bad, int* d_status,
+                            cudaStream_t stream);
+int t2t_gather_rows_strided(const void* x, long long x_row_stride, long long x_head_stride, const void* perm,
+                            void* out, int H, int N, cudaStream_t stream);
+int t2t_kmeans_maintain_strided(const void* QU, const void* KU, const void* V, long long v_row_stride,
+                                long long v_head_stride, const void* cq0, const void* ck0, void* qlab, void* cq2,
+                                void* klab, void* ck2, void* ck16, void* cks16, void* qcounts, void* qperm,
+                                void* kcounts, void* kperm, void* V_sorted, void* sumv, void* lam, float scale,
+                                int H, int N, int CQ, int C, int pin_tail, void* ws, size_t ws_bytes,
+                                int* d_status, cudaStream_t stream);
+int t2t_vstats_gather_strided(const void* V, long long v_row_stride, long long v_head_stride, const void* kperm,
+                              const void* kcounts, void* V_sorted, void* sumv, void* lam, int H, int N, int C,
+                              void* ws, size_t ws_bytes, cudaStream_t stream);
+int t2t_tile_attn_exact_strided(const void* q, long long q_row_stride, long long q_head_stride, const void* kp,
+                                const void* vp, const void* unip, const void* qperm, int* plan, int H, int N,
+                                int CQ, void* ws, size_t ws_bytes, int* d_status, cudaStream_t stream);
+int t2t_tile_attn_merge_strided(const void* QU, const void* cks, const void* sumv, const void* kcounts,
+                                const void* unip, const void* qlab, const void* qperm, const void* lam,
+                                const float* tailw, void* out, long long out_row_stride, long long out_head_stride,
+                                int H, int N, int CQ, void* ws, size_t ws_bytes, int* d_status,
+                                cudaStream_t stream);
+
 /* Tensor-core self-test: S = A . B^T, O = bf16(S / 16) . V for 128 x 128 bf16
  * operands, through the same shared-memory / TMEM operand forms the attention
  * kernels use.  No counterpart in the reference. */

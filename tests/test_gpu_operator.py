@@ -119,6 +119,40 @@ def test_caller_owned_output_tensor(small_case):
         op.step(q, k, v, state, out=mine[:, :-1])
 
 
+def test_views_of_token_major_tensors_are_read_and_written_in_place(small_case):
+    """q, k, v and the output as [H, N, 128] views of tensors stored [N, H, 128] (what a serving host holds):
+    same bits as with contiguous tensors, for a rebuild call, a reuse call and init_state."""
+    from token2tile_b200 import MaskedStepDeploy
+    c = small_case
+    H, N, CQ = c["H"], c["N"], c["CQ"]
+    q, k, v = (c[n].to(DEV) for n in "qkv")
+    token_major = lambda t: t.transpose(0, 1).contiguous().transpose(0, 1)      # [H, N, D] view of [N, H, D] storage
+    qs, ks, vs = token_major(q), token_major(k), token_major(v)
+    assert not qs.is_contiguous() and qs.stride() == (128, H * 128, 1)
+    results = []
+    for tensors, strided_out in (((q, k, v), False), ((qs, ks, vs), True)):
+        op = MaskedStepDeploy(H, N, CQ, s_frac=0.05, mask_refresh=4)
+        state = op.init_state(tensors[0], tensors[1], warm_iters=2, seed=3)
+        out = torch.zeros(N, H, 128, dtype=BF, device=DEV).transpose(0, 1) if strided_out else None
+        op.set_cfg_call(0, key=0, step=0)
+        first = op.step(*tensors, state, out=out).clone()
+        op.set_cfg_call(1, key=0, step=0)
+        second = op.step(*tensors, state, out=out).clone()
+        torch.cuda.synchronize()
+        assert op.device_status() == 0 and op.last_rebuilt is False
+        results.append((state, first.contiguous(), second.contiguous()))
+    (st_a, a1, a2), (st_b, b1, b2) = results
+    for name in ("Uq", "Uk", "ck", "cq"):
+        assert torch.equal(st_a[name].view(torch.int16), st_b[name].view(torch.int16)), name
+    assert torch.equal(a1.view(torch.int16), b1.view(torch.int16))
+    assert torch.equal(a2.view(torch.int16), b2.view(torch.int16))
+    with pytest.raises(ValueError):
+        op.step(qs[:, :, :].float(), ks, vs, state)
+    with pytest.raises(ValueError):                                      # rows that are not contiguous
+        bad = torch.zeros(H, N, 256, dtype=BF, device=DEV)[:, :, ::2]
+        op.step(bad, ks, vs, state)
+
+
 def test_init_state_projection_fit(small_case):
     from token2tile_b200 import MaskedStepDeploy
     c = small_case

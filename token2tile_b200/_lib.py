@@ -15,7 +15,7 @@ ERRORS = {1: "bad argument", 2: "CUDA launch failed", 3: "workspace too small",
           4: "shape exceeds the fixed capacity of a no-allocation entry point"}
 STATUS = {0: "ok", 1: "a bounded device wait timed out", 2: "task plan exceeded its bounds"}
 
-_P, _I, _S, _F = C.c_void_p, C.c_int, C.c_size_t, C.c_float
+_P, _I, _S, _F, _L = C.c_void_p, C.c_int, C.c_size_t, C.c_float, C.c_longlong
 
 SIGNATURES = {
     "t2t_version": (_I, []),
@@ -44,6 +44,13 @@ SIGNATURES = {
     "t2t_tile_attn_exact": (_I, [_P, _P, _P, _P, _P, _P, _I, _I, _I, _P, _S, _P, _P]),
     "t2t_tile_attn_merge": (_I, [_P] * 10 + [_I, _I, _I, _P, _S, _P, _P]),
     "t2t_tile_attn_plan_info": (_I, [_P, _I, _I, _I, _P, _P]),
+    "t2t_project_strided": (_I, [_P, _L, _L, _P, _P, _I, _I, _P, _P]),
+    "t2t_lowrank_fit_strided": (_I, [_P, _P, _L, _L, _P, _P, _I, _I, _P, _S, _P, _P, _P]),
+    "t2t_gather_rows_strided": (_I, [_P, _L, _L, _P, _P, _I, _I, _P]),
+    "t2t_kmeans_maintain_strided": (_I, [_P, _P, _P, _L, _L] + [_P] * 15 + [_F, _I, _I, _I, _I, _I, _P, _S, _P, _P]),
+    "t2t_vstats_gather_strided": (_I, [_P, _L, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P, _S, _P]),
+    "t2t_tile_attn_exact_strided": (_I, [_P, _L, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P, _S, _P, _P]),
+    "t2t_tile_attn_merge_strided": (_I, [_P] * 10 + [_L, _L, _I, _I, _I, _P, _S, _P, _P]),
     "t2t_umma_selftest": (_I, [_P, _P, _P, _P, _P, _P, _P]),
     "t2t_gather4_selftest": (_I, [_P, _I, _P, _P, _P, _P]),
     "t2t_wait_timeout_selftest": (_I, [_P, _P, _P]),

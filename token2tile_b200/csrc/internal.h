@@ -27,8 +27,10 @@ bool make_row_gather_map(void* map_out, const void* base, uint64_t rows);
 // Same matrix, box of 64 columns x `box_rows` rows: plain tile loads of contiguous rows.
 bool make_row_tile_map(void* map_out, const void* base, uint64_t rows, uint32_t box_rows);
 
-// The bf16 tensor base [heads, rows_per_head, 128] as a 3D tensor with a 64-column x `box_rows`-row x 1-head
-// box: tile loads that never cross a head, rows past the head's last row read as zeros.
-bool make_head_tile_map(void* map_out, const void* base, uint64_t rows_per_head, uint64_t heads, uint32_t box_rows);
+// A bf16 tensor of `heads` x `rows_per_head` rows of 128 elements (row (h, n) at base + h * head_stride +
+// n * row_stride, strides in elements) as a 3D tensor with a 64-column x `box_rows`-row x 1-head box: tile
+// loads that never cross a head, rows past the head's last row read as zeros.
+bool make_head_tile_map(void* map_out, const void* base, uint64_t rows_per_head, uint64_t heads, uint32_t box_rows,
+                        uint64_t row_stride, uint64_t head_stride);
 
 }  // namespace t2t

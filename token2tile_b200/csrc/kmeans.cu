@@ -320,14 +320,14 @@ __global__ void __launch_bounds__(CS_WARPS * 32) key_mean_kernel(
 __global__ void __launch_bounds__(CS_WARPS * 32) vgather_kernel(
     const __nv_bfloat16* __restrict__ V, const int* __restrict__ perm, const int* __restrict__ counts,
     const int* __restrict__ cbase, __nv_bfloat16* __restrict__ V_sorted, float* __restrict__ vsum, int N,
-    int Cn) {
+    int Cn, long long v_row_stride, long long v_head_stride) {
   const int h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int c = blockIdx.x * CS_WARPS + warp;
   if (c >= Cn) return;
   const int cnt = counts[(size_t)h * Cn + c];
   const int bs = cbase[(size_t)h * Cn + c];
   const int* srt = perm + (size_t)h * N + bs;
-  const __nv_bfloat16* Vh = V + (size_t)h * N * kD;
+  const __nv_bfloat16* Vh = V + (size_t)h * v_head_stride;      // strides in elements: V may be a view of [N, H, 128]
   __nv_bfloat16* Vs = V_sorted + ((size_t)h * N + bs) * kD;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   for (int i = 0; i < cnt; i += CS_UNR) {
@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(CS_WARPS * 32) vgather_kernel(
 #pragma unroll
     for (int u = 0; u < CS_UNR; ++u) {
       w[u] = make_uint2(0u, 0u);
-      if (i + u < cnt) w[u] = __ldcs(reinterpret_cast<const uint2*>(Vh + (size_t)srt[i + u] * kD + lane * 4));
+      if (i + u < cnt) w[u] = __ldcs(reinterpret_cast<const uint2*>(Vh + (size_t)srt[i + u] * v_row_stride + lane * 4));
     }
 #pragma unroll
     for (int u = 0; u < CS_UNR; ++u) {
@@ -386,8 +386,10 @@ __global__ void __launch_bounds__(256) vscale_kernel(const float* __restrict__ v
 
 static void launch_vstats(const __nv_bfloat16* V, const int* perm, const int* counts, const int* cbase,
                           __nv_bfloat16* V_sorted, __nv_bfloat16* sumv, float* lam, float* vsum,
-                          float* bmax, int H, int N, int Cn, cudaStream_t st) {
-  vgather_kernel<<<dim3(cdiv(Cn, CS_WARPS), H), CS_WARPS * 32, 0, st>>>(V, perm, counts, cbase, V_sorted, vsum, N, Cn);
+                          float* bmax, int H, int N, int Cn, long long v_row_stride, long long v_head_stride,
+                          cudaStream_t st) {
+  vgather_kernel<<<dim3(cdiv(Cn, CS_WARPS), H), CS_WARPS * 32, 0, st>>>(V, perm, counts, cbase, V_sorted, vsum, N, Cn,
+                                                                        v_row_stride, v_head_stride);
   vmax_kernel<<<dim3(VM_BLOCKS, H), 256, 0, st>>>(vsum, bmax, Cn);
   vscale_kernel<<<dim3(64, H), 256, 0, st>>>(vsum, bmax, sumv, lam, Cn);
 }
@@ -419,14 +421,15 @@ __global__ void __launch_bounds__(1024) bases_kernel(const int* __restrict__ cou
 // out[h, i, :] = x[h, perm[h, i], :], one thread per 16-byte chunk.
 __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ x,
                                                           const int* __restrict__ perm,
-                                                          uint4* __restrict__ out, int N, size_t total) {
+                                                          uint4* __restrict__ out, int N, size_t total,
+                                                          long long x_row_stride16, long long x_head_stride16) {
   const size_t id = (size_t)blockIdx.x * 256 + threadIdx.x;
   if (id >= total) return;
   const size_t row = id >> 4;
   const int ch = (int)(id & 15);
   const size_t h = row / N;
   const int src = perm[row];
-  out[id] = __ldcs(x + ((h * N + src) << 4) + ch);
+  out[id] = __ldcs(x + h * x_head_stride16 + (size_t)src * x_row_stride16 + ch);      // strides in 16-byte units
 }
 
 // ---------------------------------------------------------------------------
@@ -544,12 +547,13 @@ extern "C" size_t t2t_kmeans_maintain_ws_bytes(int H, int N, int CQ, int C) {
   return kmm_layout(H, N, CQ, C, nullptr).total;
 }
 
-extern "C" int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const void* cq0,
+extern "C" int t2t_kmeans_maintain_strided(const void* QU, const void* KU, const void* V, long long v_row_stride, long long v_head_stride, const void* cq0,
                                    const void* ck0, void* qlab, void* cq2, void* klab, void* ck2, void* ck16,
                                    void* cks16, void* qcounts, void* qperm, void* kcounts, void* kperm,
                                    void* V_sorted, void* sumv, void* lam, float scale, int H, int N, int CQ,
                                    int C, int pin_tail, void* ws, size_t ws_bytes, int* d_status,
                                    cudaStream_t st) {
+  if (v_row_stride < kD || v_head_stride <= 0 || (v_row_stride & 3) || (v_head_stride & 3)) return T2T_ERR_ARG;
   if (!QU || !KU || !V || !cq0 || !ck0 || !qlab || !cq2 || !klab || !ck2 || !ck16 || !cks16 || !qcounts ||
       !qperm || !kcounts || !kperm || !V_sorted || !sumv || !lam || !ws)
     return T2T_ERR_ARG;
@@ -580,8 +584,19 @@ extern "C" int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V
                                                   w.cbase_k, (const bf16*)ck0, (float*)ck2, (bf16*)ck16,
                                                   (bf16*)cks16, scale, N, C);
   launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase_k, (bf16*)V_sorted, (bf16*)sumv,
-                (float*)lam, w.vsum, w.bmax, H, N, C, st);
+                (float*)lam, w.vsum, w.bmax, H, N, C, v_row_stride, v_head_stride, st);
   return finish();
+}
+
+extern "C" int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const void* cq0,
+                                   const void* ck0, void* qlab, void* cq2, void* klab, void* ck2, void* ck16,
+                                   void* cks16, void* qcounts, void* qperm, void* kcounts, void* kperm,
+                                   void* V_sorted, void* sumv, void* lam, float scale, int H, int N, int CQ,
+                                   int C, int pin_tail, void* ws, size_t ws_bytes, int* d_status,
+                                   cudaStream_t st) {
+  return t2t_kmeans_maintain_strided(QU, KU, V, (long long)kD, (long long)N * kD, cq0, ck0, qlab, cq2, klab, ck2, ck16, cks16,
+                                     qcounts, qperm, kcounts, kperm, V_sorted, sumv, lam, scale, H, N, CQ, C, pin_tail,
+                                     ws, ws_bytes, d_status, st);
 }
 
 extern "C" size_t t2t_vstats_gather_ws_bytes(int H, int C) { return vstat_layout(H, C, nullptr).total; }
@@ -589,21 +604,36 @@ extern "C" size_t t2t_vstats_gather_ws_bytes(int H, int C) { return vstat_layout
 extern "C" int t2t_vstats_gather(const void* V, const void* kperm, const void* kcounts, void* V_sorted,
                                  void* sumv, void* lam, int H, int N, int C, void* ws, size_t ws_bytes,
                                  cudaStream_t st) {
+  return t2t_vstats_gather_strided(V, (long long)kD, (long long)N * kD, kperm, kcounts, V_sorted, sumv, lam, H, N, C, ws,
+                                   ws_bytes, st);
+}
+
+extern "C" int t2t_vstats_gather_strided(const void* V, long long v_row_stride, long long v_head_stride,
+                                         const void* kperm, const void* kcounts, void* V_sorted, void* sumv, void* lam,
+                                         int H, int N, int C, void* ws, size_t ws_bytes, cudaStream_t st) {
   if (!V || !kperm || !kcounts || !V_sorted || !sumv || !lam || !ws || H <= 0 || N <= 0 || C <= 0)
     return T2T_ERR_ARG;
+  if (v_row_stride < kD || v_head_stride <= 0 || (v_row_stride & 3) || (v_head_stride & 3)) return T2T_ERR_ARG;
   VstatWs w = vstat_layout(H, C, ws);
   if (ws_bytes < w.total) return T2T_ERR_WORKSPACE;
   bases_kernel<<<H, 1024, 0, st>>>((const int*)kcounts, w.cbase, C);
   launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase, (bf16*)V_sorted, (bf16*)sumv,
-                (float*)lam, w.vsum, w.bmax, H, N, C, st);
+                (float*)lam, w.vsum, w.bmax, H, N, C, v_row_stride, v_head_stride, st);
   return finish();
 }
 
 extern "C" int t2t_gather_rows(const void* x, const void* perm, void* out, int H, int N, cudaStream_t st) {
+  return t2t_gather_rows_strided(x, (long long)kD, (long long)N * kD, perm, out, H, N, st);
+}
+
+extern "C" int t2t_gather_rows_strided(const void* x, long long x_row_stride, long long x_head_stride,
+                                       const void* perm, void* out, int H, int N, cudaStream_t st) {
   if (!x || !perm || !out || H <= 0 || N <= 0) return T2T_ERR_ARG;
+  if (x_row_stride < kD || x_head_stride <= 0 || (x_row_stride & 7) || (x_head_stride & 7)) return T2T_ERR_ARG;
   const size_t total = (size_t)H * N * 16;
   gather_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const uint4*)x, (const int*)perm,
-                                                                     (uint4*)out, N, total);
+                                                                     (uint4*)out, N, total, x_row_stride >> 3,
+                                                                     x_head_stride >> 3);
   return finish();
 }
 
@@ -647,6 +677,6 @@ extern "C" int t2t_vstats_gather_static(const void* V, const void* kperm, const 
   // be cleared although the array keeps the previous call's contents.
   bases_kernel<<<H, 1024, 0, st>>>((const int*)kcounts, w.cbase, C);
   launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase, (bf16*)V_sorted, (bf16*)sumv,
-                (float*)lam, w.vsum, w.bmax, H, N, C, st);
+                (float*)lam, w.vsum, w.bmax, H, N, C, (long long)kD, (long long)N * kD, st);
   return finish();
 }

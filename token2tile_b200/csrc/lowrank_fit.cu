@@ -346,7 +346,15 @@ extern "C" size_t t2t_lowrank_fit_ws_bytes(int H, int N) { return fit_off_inv(H,
 
 extern "C" int t2t_lowrank_fit(const void* q, const void* k, float* Uq, float* Uk, int H, int N, void* ws,
                                size_t ws_bytes, int* d_bad, int* d_status, cudaStream_t st) {
+  return t2t_lowrank_fit_strided(q, k, (long long)kD, (long long)N * kD, Uq, Uk, H, N, ws, ws_bytes, d_bad, d_status,
+                                 st);
+}
+
+extern "C" int t2t_lowrank_fit_strided(const void* q, const void* k, long long row_stride, long long head_stride,
+                                       float* Uq, float* Uk, int H, int N, void* ws, size_t ws_bytes, int* d_bad,
+                                       int* d_status, cudaStream_t st) {
   if (!q || !k || !Uq || !Uk || !ws || !d_bad || H <= 0 || N <= 0) return T2T_ERR_ARG;
+  if (row_stride < kD || head_stride <= 0) return T2T_ERR_ARG;
   if (ws_bytes < t2t_lowrank_fit_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
   char* w = static_cast<char*>(ws);
   float* partial = reinterpret_cast<float*>(w);
@@ -358,8 +366,8 @@ extern "C" int t2t_lowrank_fit(const void* q, const void* k, float* Uq, float* U
       cudaFuncSetAttribute(lowrank_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, J_SMEM) != cudaSuccess)
     return T2T_ERR_CUDA;
   CUtensorMap mq, mk;
-  if (!make_head_tile_map(&mq, q, (uint64_t)N, (uint64_t)H, GR_ROWS) ||
-      !make_head_tile_map(&mk, k, (uint64_t)N, (uint64_t)H, GR_ROWS))
+  if (!make_head_tile_map(&mq, q, (uint64_t)N, (uint64_t)H, GR_ROWS, (uint64_t)row_stride, (uint64_t)head_stride) ||
+      !make_head_tile_map(&mk, k, (uint64_t)N, (uint64_t)H, GR_ROWS, (uint64_t)row_stride, (uint64_t)head_stride))
     return T2T_ERR_CUDA;
   gram_kernel<<<dim3(slabs, H), 128, GR_SMEM, st>>>(mq, partial, N, d_status);
   gram_kernel<<<dim3(slabs, H), 128, GR_SMEM, st>>>(mk, partial + (size_t)H * slabs * kD * kD, N, d_status);

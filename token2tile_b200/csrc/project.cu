@@ -20,6 +20,7 @@ constexpr int PJ_SMEM = PJ_SMEM_A + PJ_SMEM_B + 64 + 1024;
 __global__ void __launch_bounds__(128) project_kernel(const __nv_bfloat16* __restrict__ X,
                                                       const __nv_bfloat16* __restrict__ U,
                                                       __nv_bfloat16* __restrict__ out, int N,
+                                                      long long x_row_stride, long long x_head_stride,
                                                       int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -44,13 +45,13 @@ __global__ void __launch_bounds__(128) project_kernel(const __nv_bfloat16* __res
   }
 
   // x tile: 128 rows x 16 chunks of 16 B, 16 consecutive threads per row.
-  const __nv_bfloat16* Xh = X + (size_t)h * N * kD;
+  const __nv_bfloat16* Xh = X + (size_t)h * x_head_stride;      // strides in elements: x may be a view of [N, H, 128]
 #pragma unroll
   for (int i = 0; i < 16; ++i) {
     const int id = tid + 128 * i;
     const int row = id >> 4, ch = id & 15;
     const bool valid = row0 + row < N;
-    const __nv_bfloat16* src = valid ? Xh + (size_t)(row0 + row) * kD + ch * 8 : Xh;
+    const __nv_bfloat16* src = valid ? Xh + (size_t)(row0 + row) * x_row_stride + ch * 8 : Xh;
     cp_async16(sA + (ch >> 3) * (PJ_ROWS * 128) + sw128(row, ch & 7), src, valid ? 16u : 0u);
   }
   cp_async_commit();
@@ -240,13 +241,19 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __nv_bfloat16*
 
 extern "C" int t2t_project(const void* x, const void* U, void* out, int H, int N, int* d_status,
                            cudaStream_t stream) {
+  return t2t_project_strided(x, (long long)t2t::kD, (long long)N * t2t::kD, U, out, H, N, d_status, stream);
+}
+
+extern "C" int t2t_project_strided(const void* x, long long x_row_stride, long long x_head_stride, const void* U,
+                                   void* out, int H, int N, int* d_status, cudaStream_t stream) {
   using namespace t2t;
   if (!x || !U || !out || H <= 0 || N <= 0) return T2T_ERR_ARG;
+  if (x_row_stride < kD || x_head_stride <= 0 || (x_row_stride & 7) || (x_head_stride & 7)) return T2T_ERR_ARG;
   cudaError_t e = cudaFuncSetAttribute(project_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PJ_SMEM);
   if (e != cudaSuccess) return T2T_ERR_CUDA;
   dim3 grid(cdiv(N, PJ_ROWS), H);
   project_kernel<<<grid, 128, PJ_SMEM, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)U,
-                                                 (__nv_bfloat16*)out, N, d_status);
+                                                 (__nv_bfloat16*)out, N, x_row_stride, x_head_stride, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
 

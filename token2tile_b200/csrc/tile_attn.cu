@@ -301,7 +301,7 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
     const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
     __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
-    int* __restrict__ status) {
+    int q_row_step, int q_head_step, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
@@ -375,7 +375,8 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
     }
 
     // ---- rows of the Q tile, through qperm (slots past the task repeat its first row) --------
-    sQidx[tid] = h * N + qperm[rowbase + (tid < qrows ? tid : 0)];
+    // row of q in the [rows, 128] view of its tensor: q may be a view of [N, H, 128] (steps in 128-element rows)
+    sQidx[tid] = h * q_head_step + qperm[rowbase + (tid < qrows ? tid : 0)] * q_row_step;
 
     // ---- runs of selected, non-empty key clusters -----------------------------
     if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
@@ -658,7 +659,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
     const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
     const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
     __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
-    int* __restrict__ status) {
+    int q_row_step, int q_head_step, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
@@ -755,7 +756,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
         int r[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)      // slots past the group repeat its first row
-          r[j] = h * N + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)];
+          r[j] = h * q_head_step + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)] * q_row_step;
         if ((op & 63) == 0) mbar_arrive_expect_tx(bars + B_FULLQ + ogrp, AT_TILE);
         tma_gather4(base + ogrp * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
                     bars + B_FULLQ + ogrp);
@@ -955,7 +956,8 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
     const __nv_bfloat16* __restrict__ QU, const __nv_bfloat16* __restrict__ cks,
     const int* __restrict__ ksz, const uint32_t* __restrict__ ub,
     const int* __restrict__ qlab, const int* __restrict__ qperm, const float* __restrict__ lam_s,
-    const float* __restrict__ tailw_ptr, __nv_bfloat16* __restrict__ out, int N, int CQ,
+    const float* __restrict__ tailw_ptr, __nv_bfloat16* __restrict__ out, long long out_row_stride,
+    long long out_head_stride, int N, int CQ,
     int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -1193,7 +1195,7 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
       const float inv = 1.0f / fmaxf(ex + ph * tw, 1.0e-12f);
       const float we = bad ? 1.0f : ex * inv;
       const float wt = bad ? 0.0f : st * tw * lam * inv;
-      uint4* dst = reinterpret_cast<uint4*>(out + ((size_t)h * N + orig) * kD);
+      uint4* dst = reinterpret_cast<uint4*>(out + (size_t)h * out_head_stride + (size_t)orig * out_row_stride);
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t v[32];
@@ -1307,7 +1309,19 @@ extern "C" int t2t_tile_attn_plan(const void* tile_sizes, const void* kcounts, c
 extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp, const void* unip,
                                    const void* qperm, int* plan, int H, int N, int CQ, void* ws, size_t ws_bytes,
                                    int* d_status, cudaStream_t st) {
+  return t2t_tile_attn_exact_strided(q, (long long)kD, (long long)N * kD, kp, vp, unip, qperm, plan, H, N, CQ, ws,
+                                     ws_bytes, d_status, st);
+}
+
+extern "C" int t2t_tile_attn_exact_strided(const void* q, long long q_row_stride, long long q_head_stride,
+                                           const void* kp, const void* vp, const void* unip, const void* qperm,
+                                           int* plan, int H, int N, int CQ, void* ws, size_t ws_bytes,
+                                           int* d_status, cudaStream_t st) {
   if (!q || !kp || !vp || !unip || !qperm || !plan || !ws || H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  // q rows are fetched by TMA row gathers from a [rows, 128] view of the tensor: whole rows between rows
+  if (q_row_stride < kD || q_head_stride <= 0 || (q_row_stride % kD) || (q_head_stride % kD)) return T2T_ERR_ARG;
+  const int q_row_step = (int)(q_row_stride / kD), q_head_step = (int)(q_head_stride / kD);
+  const uint64_t q_rows = (uint64_t)(H - 1) * q_head_step + (uint64_t)(N - 1) * q_row_step + 1;
   if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
   __nv_bfloat16* attn_out;
   float* attn_lse;
@@ -1323,11 +1337,11 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   // tensor maps over q, kp, vp as [H * N, 128] matrices: the kernel fetches tile rows four at a time
   CUtensorMap mq, mk, mv;
   const uint64_t rows = (uint64_t)H * (uint64_t)N;
-  if (!cached_row_map(&mq, q, rows, 1) || !cached_row_map(&mk, kp, rows, 1) || !cached_row_map(&mv, vp, rows, 1))
+  if (!cached_row_map(&mq, q, q_rows, 1) || !cached_row_map(&mk, kp, rows, 1) || !cached_row_map(&mv, vp, rows, 1))
     return T2T_ERR_CUDA;
   // tasks above 128 rows first (one CTA per SM, two row tiles per K/V stream), then the others
   attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out,
-                                                 attn_lse, plan, H, N, CQ, d_status);
+                                                 attn_lse, plan, H, N, CQ, q_row_step, q_head_step, d_status);
   // The two kernels take disjoint tasks (own cursors, own output rows), so the second may start while the
   // first drains: it is launched with programmatic stream serialization and the first kernel releases its
   // dependents at once.  Their CTAs cannot share an SM (shared memory), so the second kernel's CTAs move in
@@ -1343,7 +1357,7 @@ extern "C" int t2t_tile_attn_exact(const void* q, const void* kp, const void* vp
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   if (cudaLaunchKernelEx(&cfg, attn_kernel, mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
-                         plan, H, N, CQ, d_status) != cudaSuccess)
+                         plan, H, N, CQ, q_row_step, q_head_step, d_status) != cudaSuccess)
     return T2T_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
@@ -1352,9 +1366,19 @@ extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* 
                                    const void* unip, const void* qlab, const void* qperm, const void* lam,
                                    const float* tailw, void* out, int H, int N, int CQ, void* ws, size_t ws_bytes,
                                    int* d_status, cudaStream_t st) {
+  return t2t_tile_attn_merge_strided(QU, cks, sumv, kcounts, unip, qlab, qperm, lam, tailw, out, (long long)kD,
+                                     (long long)N * kD, H, N, CQ, ws, ws_bytes, d_status, st);
+}
+
+extern "C" int t2t_tile_attn_merge_strided(const void* QU, const void* cks, const void* sumv, const void* kcounts,
+                                           const void* unip, const void* qlab, const void* qperm, const void* lam,
+                                           const float* tailw, void* out, long long out_row_stride,
+                                           long long out_head_stride, int H, int N, int CQ, void* ws,
+                                           size_t ws_bytes, int* d_status, cudaStream_t st) {
   if (!QU || !cks || !sumv || !kcounts || !unip || !qlab || !qperm || !lam || !tailw || !out || !ws)
     return T2T_ERR_ARG;
   if (H <= 0 || N <= 0 || CQ <= 0) return T2T_ERR_ARG;
+  if (out_row_stride < kD || out_head_stride <= 0 || (out_row_stride & 7) || (out_head_stride & 7)) return T2T_ERR_ARG;
   if (ws_bytes < t2t_tile_attn_ws_bytes(H, N)) return T2T_ERR_WORKSPACE;
   __nv_bfloat16* attn_out;
   float* attn_lse;
@@ -1365,7 +1389,7 @@ extern "C" int t2t_tile_attn_merge(const void* QU, const void* cks, const void* 
   if (!cached_row_map(&msv, sumv, (uint64_t)H * kC, TL_H)) return T2T_ERR_CUDA;
   tail_kernel<<<dim3(cdiv(N, TL_Q), H), TL_THREADS, TL_SMEM, st>>>(
       msv, attn_out, attn_lse, (const __nv_bfloat16*)QU, (const __nv_bfloat16*)cks, (const int*)kcounts, (const uint32_t*)unip, (const int*)qlab, (const int*)qperm, (const float*)lam, tailw,
-      (__nv_bfloat16*)out, N, CQ, d_status);
+      (__nv_bfloat16*)out, out_row_stride, out_head_stride, N, CQ, d_status);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
 

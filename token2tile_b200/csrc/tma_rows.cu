@@ -40,11 +40,13 @@ bool make_row_tile_map(void* map_out, const void* base, uint64_t rows, uint32_t 
             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-bool make_head_tile_map(void* map_out, const void* base, uint64_t rows_per_head, uint64_t heads, uint32_t box_rows) {
+bool make_head_tile_map(void* map_out, const void* base, uint64_t rows_per_head, uint64_t heads, uint32_t box_rows,
+                        uint64_t row_stride, uint64_t head_stride) {
   EncodeTiledFn fn = encode_tiled();
   if (!fn || (reinterpret_cast<uintptr_t>(base) & 15u) || box_rows == 0 || box_rows > 256) return false;
+  if ((row_stride & 7u) || (head_stride & 7u)) return false;      // TMA strides are multiples of 16 bytes
   const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)rows_per_head, (cuuint64_t)heads};
-  const cuuint64_t strides[2] = {(cuuint64_t)kD * 2, (cuuint64_t)kD * 2 * rows_per_head};
+  const cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)head_stride * 2};
   const cuuint32_t box[3] = {64, box_rows, 1};
   const cuuint32_t elem[3] = {1, 1, 1};
   return fn(reinterpret_cast<CUtensorMap*>(map_out), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base),

@@ -64,7 +64,13 @@ def lowrank_fit(q, k, r=32, *, check_finite=True):
     lib = _lib.load()
     qb = q if q.dtype == BF16 else q.to(BF16)
     kb = k if k.dtype == BF16 else k.to(BF16)
-    qb, kb = qb.contiguous(), kb.contiguous()
+    try:                                    # views of [N, H, 128] tensors are read in place
+        lay = rows_layout(qb)
+        if rows_layout(kb) != lay:
+            raise ValueError("q and k are laid out differently")
+    except ValueError:
+        qb, kb = qb.contiguous(), kb.contiguous()
+        lay = rows_layout(qb)
     H, N, D = qb.shape
     dev = qb.device
     Uq = torch.zeros(H, D, r, device=dev, dtype=torch.float32)
@@ -72,8 +78,9 @@ def lowrank_fit(q, k, r=32, *, check_finite=True):
     flags = torch.zeros(2 * H + 1, device=dev, dtype=torch.int32)       # [2 H] non-finite, [1] wait status
     ws = torch.empty(int(lib.t2t_lowrank_fit_ws_bytes(H, N)), device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
-        check(lib.t2t_lowrank_fit(ptr(qb), ptr(kb), ptr(Uq), ptr(Uk), H, N, ptr(ws), ws.numel(), ptr(flags),
-                                  ptr(flags) + 8 * H, _stream_ptr(torch.cuda.current_stream(dev))), "t2t_lowrank_fit")
+        check(lib.t2t_lowrank_fit_strided(ptr(qb), ptr(kb), lay[0], lay[1], ptr(Uq), ptr(Uk), H, N, ptr(ws), ws.numel(),
+                                          ptr(flags), ptr(flags) + 8 * H,
+                                          _stream_ptr(torch.cuda.current_stream(dev))), "t2t_lowrank_fit")
     if check_finite:
         f = flags.cpu()
         if int(f[2 * H]) != 0:
@@ -102,6 +109,22 @@ def online_u(qf, kf, r=32):
 
 def _stream_ptr(stream) -> int:
     return stream.cuda_stream
+
+
+def rows_layout(t):
+    """(row stride, head stride) in elements of a bfloat16 tensor indexed [head, row, 128] whose 128
+    elements of a row are contiguous: (128, N * 128) for a contiguous [H, N, 128] tensor, (H * 128, 128) for
+    the [H, N, 128] view of a tensor stored [N, H, 128].  The kernels take both; strides must be whole rows
+    (multiples of 128 elements) and the storage 16-byte aligned."""
+    if t.dim() != 3 or t.shape[2] != 128 or t.dtype != BF16 or t.stride(2) != 1:
+        raise ValueError(f"expected a bfloat16 [H, n, 128] tensor with contiguous rows, got {t.dtype} "
+                         f"{tuple(t.shape)} strides {tuple(t.stride())}")
+    head, row = t.stride(0), t.stride(1)
+    if t.shape[0] == 1:
+        head = max(head, 128)            # the stride of a singleton dimension is arbitrary
+    if row % 128 or head % 128 or row <= 0 or head <= 0 or t.data_ptr() % 16:
+        raise ValueError(f"row and head strides must be positive multiples of 128 elements, got {tuple(t.stride())}")
+    return row, head
 
 
 # ---------------------------------------------------------------------------
@@ -274,12 +297,14 @@ class MaskedStepDeploy:
         }
 
     def _check_qkv(self, *tensors):
+        """q, k, v (and a caller's output tensor): bfloat16 [H, N, 128] on the operator's device, contiguous or
+        a view with whole-row strides (the [H, N, 128] view of a [N, H, 128] tensor: see rows_layout)."""
         for t in tensors:
-            if t.dtype != BF16 or tuple(t.shape) != (self.H, self.N, self.D) or not t.is_contiguous() \
-                    or t.device != self.QU.device:
+            if t.dtype != BF16 or tuple(t.shape) != (self.H, self.N, self.D) or t.device != self.QU.device:
                 raise ValueError(
-                    f"expected contiguous bfloat16 [{self.H}, {self.N}, {self.D}] on {self.QU.device}, got "
+                    f"expected bfloat16 [{self.H}, {self.N}, {self.D}] on {self.QU.device}, got "
                     f"{t.dtype} {tuple(t.shape)} on {t.device}")
+            rows_layout(t)
 
     # -- stage timing ------------------------------------------------------------
     def _mark(self, name):
@@ -300,7 +325,9 @@ class MaskedStepDeploy:
 
     # -- kernel wrappers -------------------------------------------------------
     def _project(self, x, U, out, st):
-        check(self.lib.t2t_project(ptr(x), ptr(U), ptr(out), self.H, self.N, ptr(self.status), st), "t2t_project")
+        row, head = rows_layout(x)
+        check(self.lib.t2t_project_strided(ptr(x), row, head, ptr(U), ptr(out), self.H, self.N, ptr(self.status), st),
+              "t2t_project")
 
     def _assign(self, x, cen, labels, st):
         check(self.lib.t2t_assign(ptr(x), ptr(cen), ptr(labels), self.H, self.N, cen.shape[1], -1, 0,
@@ -394,7 +421,9 @@ class MaskedStepDeploy:
 
     # -- the attention call ------------------------------------------------------
     def step(self, q, k, v, state, out=None):
-        """q, k, v: [H, N, 128] bfloat16 contiguous, original row order.  state:
+        """q, k, v: [H, N, 128] bfloat16, original row order; contiguous, or views with whole-row
+        strides (the [H, N, 128] view of a tensor stored [N, H, 128], which a serving host holds,
+        is read in place: no transposing copy).  state:
         dict(Uq, Uk, ck, cq); ck / cq are replaced by the centroids that
         warm-start the next call.  Returns out [H, N, 128] bfloat16: the tensor
         passed as `out` (same shape, dtype, device, contiguous), else a buffer
@@ -405,9 +434,13 @@ class MaskedStepDeploy:
         self.check_status(wait=False)
         if out is None:
             out = self.tile_attn_out
-        elif (out.shape != self.tile_attn_out.shape or out.dtype != BF16 or out.device != self.tile_attn_out.device
-              or not out.is_contiguous()):
-            raise ValueError("out must be a contiguous bfloat16 tensor [H, N, 128] on the operator's device")
+        else:
+            try:
+                self._check_qkv(out)
+            except ValueError as exc:
+                raise ValueError("out must be a bfloat16 tensor [H, N, 128] on the operator's device, contiguous or "
+                                 f"with whole-row strides ({exc})") from None
+        q_lay, k_lay, v_lay, o_lay = rows_layout(q), rows_layout(k), rows_layout(v), rows_layout(out)
         caller = torch.cuda.current_stream(self.dev)
         if caller != self.s_main:
             self.s_main.wait_stream(caller)
@@ -423,8 +456,8 @@ class MaskedStepDeploy:
                 self._project(k, state["Uk"], self.KU, st)
                 self._mark("project")
                 ck16 = torch.empty(H, C, self.r, device=self.dev, dtype=BF16)
-                check(L.t2t_kmeans_maintain(
-                    ptr(self.QU), ptr(self.KU), ptr(v), ptr(state["cq"]), ptr(state["ck"]),
+                check(L.t2t_kmeans_maintain_strided(
+                    ptr(self.QU), ptr(self.KU), ptr(v), v_lay[0], v_lay[1], ptr(state["cq"]), ptr(state["ck"]),
                     ptr(S["qlab"]), ptr(self._kmm_cq2), ptr(S["klab"]), ptr(self._kmm_ck2), ptr(ck16),
                     ptr(S["cks"]), ptr(S["tile_sizes"]), ptr(S["qperm"]), ptr(S["counts"]), ptr(S["kperm"]),
                     ptr(self.vp), ptr(self._kmm_sumv), ptr(self._kmm_lam), self.scale, H, N, CQ, C,
@@ -436,8 +469,8 @@ class MaskedStepDeploy:
                 # the key gather only needs kperm: it runs on the side stream, under the selection
                 # (one is bound by HBM, the other by integer arithmetic)
                 self.s_side.wait_stream(self.s_main)
-                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, _stream_ptr(self.s_side)),
-                      "t2t_gather_rows")
+                check(L.t2t_gather_rows_strided(ptr(k), k_lay[0], k_lay[1], ptr(S["kperm"]), ptr(self.kp), H, N,
+                                                _stream_ptr(self.s_side)), "t2t_gather_rows")
                 check(L.t2t_score_select_union(
                     ptr(self.QU), ptr(S["cks"]), ptr(S["counts"]), ptr(S["qperm"]), ptr(S["tile_sizes"]),
                     ptr(self.ns_t), ptr(S["unip"]), ptr(self.rowcnt), H, N, CQ, self.pin_tail, ptr(self._ws),
@@ -458,20 +491,22 @@ class MaskedStepDeploy:
                 # QU and the stored centroids share a basis
                 self._project(q, S["Uq"], self.QU, st)
                 self._mark("project")
-                check(L.t2t_gather_rows(ptr(k), ptr(S["kperm"]), ptr(self.kp), H, N, st), "t2t_gather_rows")
+                check(L.t2t_gather_rows_strided(ptr(k), k_lay[0], k_lay[1], ptr(S["kperm"]), ptr(self.kp), H, N, st),
+                      "t2t_gather_rows")
                 self._mark("gather_k")
-                check(L.t2t_vstats_gather(ptr(v), ptr(S["kperm"]), ptr(S["counts"]), ptr(self.vp),
+                check(L.t2t_vstats_gather_strided(ptr(v), v_lay[0], v_lay[1], ptr(S["kperm"]), ptr(S["counts"]), ptr(self.vp),
                                           ptr(self._kmm_sumv), ptr(self._kmm_lam), H, N, C, ptr(self._ws),
                                           self._ws.numel(), st), "t2t_vstats_gather")
                 self._mark("vstats")
             # the plan belongs to the structure: a reuse call only resets its task cursor
-            check(L.t2t_tile_attn_exact(
-                ptr(q), ptr(self.kp), ptr(self.vp), ptr(S["unip"]), ptr(S["qperm"]), ptr(S["tile_attn_plan"]),
+            check(L.t2t_tile_attn_exact_strided(
+                ptr(q), q_lay[0], q_lay[1], ptr(self.kp), ptr(self.vp), ptr(S["unip"]), ptr(S["qperm"]),
+                ptr(S["tile_attn_plan"]),
                 H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_exact")
             self._mark("attn_exact")
-            check(L.t2t_tile_attn_merge(
+            check(L.t2t_tile_attn_merge_strided(
                 ptr(self.QU), ptr(S["cks"]), ptr(self._kmm_sumv), ptr(S["counts"]), ptr(S["unip"]),
-                ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(out),
+                ptr(S["qlab"]), ptr(S["qperm"]), ptr(self._kmm_lam), ptr(self.tailw_t), ptr(out), o_lay[0], o_lay[1],
                 H, N, CQ, ptr(self._attn_ws), self._attn_ws.numel(), ptr(self.status), st), "t2t_tile_attn_merge")
             self._mark("residual_merge")
             # the status word travels to pinned host memory behind the kernels; nobody waits for it here

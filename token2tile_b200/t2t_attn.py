@@ -758,8 +758,15 @@ def _get_h3_runtime(used_tokens: int, device, heads: int = 28, video_tokens=None
 # the per-layer implementation
 # ---------------------------------------------------------------------------
 def _heads_major(x):
-    """[N, H, D] view -> contiguous [H, N, D] in the kernels' dtype."""
-    return x.transpose(0, 1).to(KERNEL_DTYPE).contiguous()
+    """[N, H, D] tensor -> [H, N, D] in the kernels' dtype WITHOUT a copy where possible: the kernels read
+    whole-row strided views in place (the reference transposes and copies q, k and v here,
+    t2t_attn.py:1161-1163).  A tensor of another dtype, with non-contiguous rows or on the CPU stand-in
+    path is converted to a contiguous [H, N, D] copy as before."""
+    view = x.transpose(0, 1)
+    if x.dtype == KERNEL_DTYPE and x.is_cuda and x.stride(-1) == 1 and x.stride(0) % 128 == 0 \
+            and x.stride(1) % 128 == 0 and x.data_ptr() % 16 == 0:
+        return view
+    return view.to(KERNEL_DTYPE).contiguous()
 
 
 class T2TAttentionImpl(AttentionImpl):
@@ -855,6 +862,12 @@ class T2TAttentionImpl(AttentionImpl):
                                           seed=self.layer_idx * 2 + parity)
                 cache.states[state_key] = state
             previous = {name: state[name].clone() for name in ("ck", "cq")}
+            if query.dtype == KERNEL_DTYPE and q.is_cuda and hasattr(deploy, "tile_attn_out"):
+                # the operator writes its result straight into the host's [1, N, H, D] layout
+                result = torch.empty_like(query)
+                deploy.step(q, k, v, state, out=result[0].transpose(0, 1))
+                _sanitize_state(state, previous)
+                return result
             output = deploy.step(q, k, v, state)
             _sanitize_state(state, previous)
         return output.transpose(0, 1).unsqueeze(0).to(query.dtype).contiguous()
