@@ -43,7 +43,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     procs = []
     for src in SOURCES:
         obj = CSRC / (src[:-3] + ".o")
-        cmd = [_nvcc(), *NVCC_FLAGS, f"-I{INCLUDE}", f"-I{CSRC}", "-c", str(CSRC / src), "-o", str(obj)]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("T2T_NVCC_EXTRA", "").split(), f"-I{INCLUDE}", f"-I{CSRC}", "-c",
+               str(CSRC / src), "-o", str(obj)]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))

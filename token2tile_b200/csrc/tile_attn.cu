@@ -290,280 +290,84 @@ __device__ __forceinline__ bool build_runs(const int* __restrict__ koh, const ui
   return *abort_flag == 0;
 }
 
-// ---------------------------------------------------------------------------
-// exact attention over the unions
-// ---------------------------------------------------------------------------
-constexpr int AT_TILE = KT * kD * 2;   // 32 KB
-constexpr int AT_SMEM_INTS = 5 * KT + 2 * MAX_RUNS + 8 + 32;
-constexpr int AT_SMEM = 3 * AT_TILE + 64 + AT_SMEM_INTS * 4 + 1024;
+#ifdef T2T_PROF
+__device__ unsigned long long g_prof[32];
+__device__ long long g_prof_mid;
+#define PROF_NOW() clock64()
+#define PROF_ADD(i, v) atomicAdd(&g_prof[i], (unsigned long long)(v))
+#else
+#define PROF_NOW() 0ll
+#define PROF_ADD(i, v) do { } while (0)
+#endif
+#ifndef T2T_POLY
+#define T2T_POLY 0
+#endif
+constexpr int AT_TILE = KT * kD * 2;   // 32 KB: one 128-row tile of q, kp or vp
 
-__global__ void __launch_bounds__(128, 2) attn_kernel(
-    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-    const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
-    __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
-    int q_row_step, int q_head_step, int* __restrict__ status) {
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
-  const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 2 * AT_TILE;
-  // [0] S ready, [1] O ready, [2] K tile landed, [3] V tile landed, [4] Q tile landed
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + 3 * AT_TILE);
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + 3 * AT_TILE + 40);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + 3 * AT_TILE + 48);
-  int* sInt = reinterpret_cast<int*>(sm + 3 * AT_TILE + 64);
-  int* sGidx = sInt;                    // [4][KT] row of kp/vp (all heads) for every key slot of a tile
-  int* sQidx = sInt + 4 * KT;           // [KT] row of q for every query slot of the task
-  int* sRunStart = sInt + 5 * KT;       // [MAX_RUNS]
-  int* sRunCum = sRunStart + MAX_RUNS;  // [MAX_RUNS + 1]
-  int* sMisc = sRunCum + MAX_RUNS + 8;  // [0] task, [1] runs; scan scratch from [8]
-
-  const PlanView pv = plan_view(plan, H, N, CQ);
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-  if (warp == 0) {
-    tmem_alloc(tmem_slot, 256);
-    tmem_relinquish();
+// kp / vp rows (all heads: `row0` is the head's first row) of union positions p0 .. p0 + 3, from the run list of
+// build_runs.  `cursor` is the caller's run index from its previous, smaller p0 (0 at the start of a task): the
+// run of p0 is found by stepping forward from it.  Positions past the union read the head's first row (their
+// scores are masked).  Returns whether the four rows exist and are consecutive rows of kp / vp.
+__device__ __forceinline__ bool union_rows(const int* sRunStart, const int* sRunCum, int nruns, int kvlen, int p0,
+                                           int row0, int& cursor, int (&r)[4]) {
+  int ru = cursor;
+  while (ru + 1 < nruns && sRunCum[ru + 1] <= p0) ++ru;
+  cursor = ru;
+  int next = sRunCum[ru + 1];
+  int row = sRunStart[ru] + p0 - sRunCum[ru];
+  r[0] = p0 < kvlen ? row0 + row : row0;
+#pragma unroll
+  for (int j = 1; j < 4; ++j) {
+    const int p = p0 + j;
+    if (p >= next && ru + 1 < nruns) {
+      ++ru;
+      row = sRunStart[ru];
+      next = sRunCum[ru + 1];
+    } else {
+      ++row;
+    }
+    r[j] = p < kvlen ? row0 + row : row0;
   }
-  if (tid == 0) {
-    *abort_flag = 0;
-    for (int i = 0; i < 5; ++i) mbar_init(bars + i, 1);
-    mbar_init_fence();
+  return p0 + 3 < kvlen && r[3] == r[0] + 3;
+}
+
+// Tensor maps over kp and vp as [H * N, 128] matrices with boxes of 1, 32 and 64 rows by 64 columns.
+struct KVMaps {
+  CUtensorMap k1, k32, k64, v1, v32, v64;
+};
+
+// One 64-column block of a 128-row K or V tile, fetched by a whole warp.  Lane g owns destination rows
+// 4 g .. 4 g + 3, whose source rows are r[0..3]; `whole` says that they are four consecutive rows of kp / vp.
+// Groups that follow each other in the source as well form a stretch, and a stretch is fetched with 64-row
+// tile loads, then 32-row tile loads, then four-row gathers for what is left (a tile load moves 2.6x / 1.8x
+// the bytes per cycle of a gather; a swizzled tile may start at any multiple of four rows, the pattern being a
+// function of the shared-memory address).  Groups that straddle two runs of the union are gathered.
+// `dst` is the block's first byte; every instruction counts its bytes on `full`.
+__device__ __forceinline__ void fetch_block(uint32_t dst, const CUtensorMap* map1, const CUtensorMap* map32,
+                                            const CUtensorMap* map64, int col, const int (&r)[4], bool whole,
+                                            int lane, uint64_t* full) {
+  const int prev = __shfl_up_sync(0xffffffffu, r[0], 1);
+  const unsigned wmask = __ballot_sync(0xffffffffu, whole);
+  const bool linked = whole && lane > 0 && ((wmask >> (lane - 1)) & 1u) && r[0] == prev + 4;
+  const unsigned lmask = __ballot_sync(0xffffffffu, linked);      // bit g: group g continues the stretch of g - 1
+  const uint32_t mine = dst + lane * 512;
+  if (whole) {
+    const unsigned upto = 0xffffffffu >> (31 - lane);
+    const int start = 31 - __clz((wmask & ~lmask) & upto);
+    const unsigned above = ~lmask & ~upto;
+    const int end = above ? __ffs(above) - 1 : 32;
+    const int len = end - start, k = lane - start;
+    const int k64 = len & ~15, k32 = k64 + ((len - k64) & ~7);
+    if (k < k64) {
+      if ((k & 15) == 0) tma_load_tile(mine, map64, col, r[0], full);
+      return;
+    }
+    if (k < k32) {
+      if (((k - k64) & 7) == 0) tma_load_tile(mine, map32, col, r[0], full);
+      return;
+    }
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = *tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 128;
-  uint32_t phK = 0, phV = 0, phQ = 0;      // used by thread 0 only
-  const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
-  uint32_t phS = 0, phO = 0;
-  const int numTasks = pv.counters[0];
-  const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
-  constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
-  constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
-
-  // Tile loads: 64 TMA instructions per 128-row tile, each four rows of one 64-column block.  Threads
-  // 0..63 issue the K tile's, threads 64..127 the V (or Q) tile's.
-  const int ld_i = tid & 63, ld_blk = ld_i >> 5, ld_grp = ld_i & 31;
-  const uint32_t ld_off = ld_blk * (KT * 128) + ld_grp * 512;
-  auto gather_tile = [&](uint32_t dst, const CUtensorMap* map, const int* rows, uint64_t* bar) {
-    if (ld_i == 0) mbar_arrive_expect_tx(bar, AT_TILE);
-    const int4 r = reinterpret_cast<const int4*>(rows)[ld_grp];
-    tma_gather4(dst + ld_off, map, ld_blk * 64, r.x, r.y, r.z, r.w, bar);
-  };
-
-  while (true) {
-    __syncthreads();
-    if (tid == 0) {      // next task of at most QT rows (the two-tile kernel takes the others)
-      int i;
-      do { i = atomicAdd(&pv.counters[1], 1); } while (i < numTasks && pv.tasks[i].w > QT);
-      sMisc[0] = i;
-    }
-    __syncthreads();
-    const int ti = sMisc[0];
-    if (ti >= numTasks || *abort_flag) break;
-    const int4 tk = pv.tasks[ti];
-    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
-    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
-    const size_t rowbase = (size_t)h * N + qs;
-
-    if (kvlen == 0) {   // empty union: O = 0, lse = -inf
-      for (int i = tid; i < qrows * 16; i += 128)
-        reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
-      for (int r = tid; r < qrows; r += 128) attn_lse[rowbase + r] = -INFINITY;
-      continue;
-    }
-
-    // ---- rows of the Q tile, through qperm (slots past the task repeat its first row) --------
-    // row of q in the [rows, 128] view of its tensor: q may be a view of [N, H, 128] (steps in 128-element rows)
-    sQidx[tid] = h * q_head_step + qperm[rowbase + (tid < qrows ? tid : 0)] * q_row_step;
-
-    // ---- runs of selected, non-empty key clusters -----------------------------
-    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
-                    pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
-      break;
-    const int nruns = sMisc[1];
-    const int ntiles = cdiv(kvlen, KT);
-
-    auto key_row = [&](int p) -> int {   // kp/vp row (all heads) of the p-th token of the union
-      if (p >= kvlen) return h * N;     // slots past the union read a real row; their scores are masked
-      int lo = 0, hi = nruns - 1;
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (sRunCum[mid] <= p) lo = mid; else hi = mid - 1;
-      }
-      return h * N + sRunStart[lo] + p - sRunCum[lo];
-    };
-    sGidx[tid] = key_row(tid);
-    sGidx[KT + tid] = key_row(KT + tid);
-    sGidx[2 * KT + tid] = key_row(2 * KT + tid);
-    __syncthreads();
-    if (tid < 64) gather_tile(sK, &mapK, sGidx, bars + 2);
-    else gather_tile(sQ, &mapQ, sQidx, bars + 4);
-    auto issue_qk = [&]() {      // thread 0: S = Q K^T once the K tile has landed
-      if (!mbar_wait(bars + 2, phK, abort_flag)) return;
-      phK ^= 1u;
-      tc_fence_after();
-#pragma unroll
-      for (int s = 0; s < 8; ++s) {
-        const uint64_t ad = make_sdesc(sQ + (s >> 2) * (QT * 128) + (s & 3) * 32, 16, 1024);
-        const uint64_t bd = make_sdesc(sK + (s >> 2) * (KT * 128) + (s & 3) * 32, 16, 1024);
-        umma_ss(tS, ad, bd, idescQK, s > 0 ? 1u : 0u);
-      }
-      umma_commit(bars + 0);
-    };
-    if (tid == 0) {
-      tc_fence_after();
-      if (mbar_wait(bars + 4, phQ, abort_flag)) {
-        phQ ^= 1u;
-        issue_qk();
-      }
-    }
-
-    RowState rs;
-    rs.m = -INFINITY;
-    rs.l = 0.f;
-    bool dead = false;
-
-    for (int t = 0; t < ntiles; ++t) {
-      const int* gcur = sGidx + (t & 3) * KT;
-      const int* gnxt = sGidx + ((t + 1) & 3) * KT;
-      if (!mbar_wait(bars + 0, phS, abort_flag)) { dead = true; break; }
-      phS ^= 1u;
-      if (t > 0) {
-        if (!mbar_wait(bars + 1, phO, abort_flag)) { dead = true; break; }
-        phO ^= 1u;
-      }
-      tc_fence_after();
-      // K tile and V tile buffers are free now
-      const bool more = t + 1 < ntiles;
-      if (tid >= 64) gather_tile(sV, &mapV, gcur, bars + 3);
-      else if (more) gather_tile(sK, &mapK, gnxt, bars + 2);
-
-      // ---- softmax of this thread's row --------------------------------------
-      float s[KT];
-      {
-        uint32_t v0[32], v1[32], v2[32], v3[32];
-        tmem_ld32(tS_lane, v0);
-        tmem_ld32(tS_lane + 32, v1);
-        tmem_ld32(tS_lane + 64, v2);
-        tmem_ld32(tS_lane + 96, v3);
-        tmem_wait_ld();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          s[j] = __uint_as_float(v0[j]);
-          s[32 + j] = __uint_as_float(v1[j]);
-          s[64 + j] = __uint_as_float(v2[j]);
-          s[96 + j] = __uint_as_float(v3[j]);
-        }
-      }
-      const int valid = kvlen - t * KT;
-      if (valid < KT) {
-#pragma unroll
-        for (int j = 0; j < KT; ++j) if (j >= valid) s[j] = -INFINITY;
-      }
-      float mx4[4] = {s[0], s[1], s[2], s[3]};      // independent chains: a single one is 127 dependent ops
-#pragma unroll
-      for (int j = 4; j < KT; j += 4) {
-        mx4[0] = fmaxf(mx4[0], s[j]); mx4[1] = fmaxf(mx4[1], s[j + 1]);
-        mx4[2] = fmaxf(mx4[2], s[j + 2]); mx4[3] = fmaxf(mx4[3], s[j + 3]);
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
-      if (t == 0) {
-        rs.m = mx;
-      } else {
-        const bool grow = mx > rs.m + kLazy;
-        if (__any_sync(0xffffffffu, grow)) {
-          const float mnew = grow ? mx : rs.m;
-          const float alpha = ex2_approx(rs.m - mnew);
-          rescale_rows(tO_lane, alpha);
-          rs.l *= alpha;
-          rs.m = mnew;
-        }
-      }
-      const float nm = -rs.m;
-      float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[KT / 2];
-#pragma unroll
-      for (int j = 0; j < KT / 2; ++j) {
-        const float p0 = ex2_approx(fmaf(s[2 * j], sc, nm));
-        const float p1 = ex2_approx(fmaf(s[2 * j + 1], sc, nm));
-        ls4[j & 3] += p0 + p1;
-        pk[j] = pack_bf2(p0, p1);
-      }
-      const float lsum = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-      rs.l += lsum;
-      {
-        uint32_t lo[32], hi[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) { lo[j] = pk[j]; hi[j] = pk[32 + j]; }
-        tmem_st32(tS_lane, lo);
-        tmem_st32(tS_lane + 32, hi);
-      }
-      tmem_wait_st();
-      tc_fence_before();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-        if (mbar_wait(bars + 3, phV, abort_flag)) {      // V(t) has landed
-          phV ^= 1u;
-#pragma unroll
-          for (int s8 = 0; s8 < 8; ++s8) {
-            const uint64_t bd = make_sdesc(sV + s8 * 2048, KT * 128, 1024);
-            umma_ts(tO, tS + s8 * 8, bd, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
-          }
-          umma_commit(bars + 1);
-          if (more) issue_qk();
-        }
-      }
-      // Rows of tile t + 3, while the tensor core works.  Their buffer was last read in iteration t - 1,
-      // and the barrier of iteration t + 1 orders this write before its first reader (iteration t + 2).
-      if (t + 3 < ntiles) sGidx[((t + 3) & 3) * KT + tid] = key_row((t + 3) * KT + tid);
-    }
-    if (!dead) {
-      if (!mbar_wait(bars + 1, phO, abort_flag)) dead = true;
-      else phO ^= 1u;
-    }
-    if (dead) break;
-    tc_fence_after();
-    {
-      const float inv = 1.0f / rs.l;
-      const bool wr = tid < qrows;
-      uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + tid) * kD);
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld32(tO_lane + c * 32, v);
-        tmem_wait_ld();
-        if (wr) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 o;
-            o.x = pack_bf2(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
-            o.y = pack_bf2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
-            o.z = pack_bf2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
-            o.w = pack_bf2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
-            dst[c * 4 + g] = o;
-          }
-        }
-      }
-      if (wr) attn_lse[rowbase + tid] = (rs.m + log2f(rs.l)) * 0.6931471805599453f;
-    }
-    tc_fence_before();
-  }
-  if (*abort_flag) {
-    if (tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
-    // a wait gave up: let tile copies still in flight land before the shared memory is released
-    for (int i = 0; i < 100; ++i) __nanosleep(1000);
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, 256);
-  // This kernel may have started while the kernel launched before it (the tasks above QT rows) was still
-  // running.  No CTA leaves before that grid has completed and its results are visible, so that this grid's
-  // completion, which later work in the stream waits for, implies the other's.  (Without a programmatic
-  // launch the instruction returns at once.)
-  asm volatile("griddepcontrol.wait;\n" ::: "memory");
+  tma_gather4(mine, map1, col, r[0], r[1], r[2], r[3], full);
 }
 
 // ---------------------------------------------------------------------------
@@ -587,13 +391,28 @@ __global__ void __launch_bounds__(128, 2) attn_kernel(
 // fullQ[g].  Ring slot s holds tile g with g & 1 == s, where g counts the tiles this
 // CTA has processed; the n-th fill of a slot waits for phase n of its free barrier
 // (phase 0 is completed at start-up) and completes phase n of its full barrier.
-// Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so
-// that few registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16
-// over the columns S occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always
-// columns that were read before).  MASK: columns >= valid lie past the union and count as -inf.
-template <bool MASK>
-__device__ __forceinline__ void softmax_tile_2pass(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid,
-                                                   bool first, float sc) {
+// 2^x for x <= 8 without the special-function unit: round x to the nearest integer n (the magic-number add
+// leaves n in the low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, well inside a
+// bf16 rounding step), and n added to the exponent field.  Inputs below -125 count as -125 (2^-125 ~ 0).
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;      // 1.5 * 2^23
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(0.055171408f, f, 0.24261075f);
+  p = fmaf(p, f, 0.69326097f);
+  p = fmaf(p, f, 0.99992812f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so that few
+// registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16 over the columns S
+// occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always columns that were read
+// before).  One exponential in POLY (0: none) runs on the FMA pipe instead of the special-function unit, whose
+// 16 results per cycle and SM are what bounds two row groups that compute at the same time.  MASK: columns
+// >= valid lie past the union and count as -inf.
+template <bool MASK, int POLY>
+__device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid, bool first,
+                                             float sc, long long* prof_mid = nullptr) {
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -621,6 +440,9 @@ __device__ __forceinline__ void softmax_tile_2pass(uint32_t tS_lane, uint32_t tO
     }
   }
   const float nm = -rs.m;
+#ifdef T2T_PROF
+  if (prof_mid) *prof_mid = clock64();
+#endif
   float ls4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -635,8 +457,9 @@ __device__ __forceinline__ void softmax_tile_2pass(uint32_t tS_lane, uint32_t tO
         if (c * 32 + 2 * j >= valid) x0 = -INFINITY;
         if (c * 32 + 2 * j + 1 >= valid) x1 = -INFINITY;
       }
-      const float p0 = ex2_approx(fmaf(x0, sc, nm));
-      const float p1 = ex2_approx(fmaf(x1, sc, nm));
+      const float y0 = fmaf(x0, sc, nm), y1 = fmaf(x1, sc, nm);
+      const float p0 = (POLY > 0 && (2 * j) % POLY == POLY - 1) ? exp2_fma(y0) : ex2_approx(y0);
+      const float p1 = (POLY > 0 && (2 * j + 1) % POLY == POLY - 1) ? exp2_fma(y1) : ex2_approx(y1);
       ls4[j & 3] += p0 + p1;
       pk[j] = pack_bf2(p0, p1);
     }
@@ -650,14 +473,13 @@ constexpr int A2_THREADS = (10 + A2_COPY_WARPS) * 32;   // 8 softmax warps, the 
 constexpr int A2_SLOT = 2 * AT_TILE;                      // K tile, V tile
 constexpr int A2_OFF_SLOT = 2 * AT_TILE;                  // after the two Q tiles
 constexpr int A2_OFF_MISC = A2_OFF_SLOT + 2 * A2_SLOT;
-constexpr int A2_MAX_TILES = 1024;                        // tiles with a precomputed first run
-constexpr int A2_SMEM_INTS = A2_MAX_TILES + 8 + 2 * MAX_RUNS + 8 + 32;
+constexpr int A2_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
 constexpr int A2_SMEM = A2_OFF_MISC + 256 + A2_SMEM_INTS * 4 + 1024;
 enum { B_S = 0, B_O = 2, B_P = 4, B_FULLK = 6, B_FULLV = 8, B_FREEK = 10, B_FREEV = 12, B_FULLQ = 14, B_COUNT = 16 };
 
 __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
-    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
-    const __grid_constant__ CUtensorMap mapV, const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
+    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ KVMaps maps,
+    const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
     __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
     int q_row_step, int q_head_step, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
@@ -667,8 +489,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + A2_OFF_MISC + B_COUNT * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + A2_OFF_MISC + B_COUNT * 8 + 8);
   int* sInt = reinterpret_cast<int*>(sm + A2_OFF_MISC + 256);
-  int* sTileRun = sInt;                           // [A2_MAX_TILES + 1] run that holds the first key of a tile
-  int* sRunStart = sInt + A2_MAX_TILES + 8;       // [MAX_RUNS]
+  int* sRunStart = sInt;                          // [MAX_RUNS]
   int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
   int* sMisc = sRunCum + MAX_RUNS + 8;            // [0] task, [1] runs; scan scratch from [8]
 
@@ -733,60 +554,43 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
     const int ntiles = cdiv(kvlen, KT);
     const int rows0 = (qrows + 1) >> 1;                       // rows of group 0; group 1 takes the rest
     const uint32_t g0 = tiles_done;
-    auto run_of = [&](int p, int lo, int hi) -> int {         // last run in [lo, hi] that starts at or before p
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (sRunCum[mid] <= p) lo = mid; else hi = mid - 1;
-      }
-      return lo;
-    };
-    // run of the first key of every tile: narrows the per-row searches of the copy warp
-    for (int i = tid; i <= ntiles && i <= A2_MAX_TILES; i += A2_THREADS)
-      sTileRun[i] = i < ntiles ? run_of(i * KT, 0, nruns - 1) : nruns - 1;
-    __syncthreads();
 
-    if (warp >= 10) {
+    if (warp >= 10 && warp < 14) {
       // ================= copy warps: Q tiles of both groups, then the K / V stream ===============
-      const int cw = warp - 10;
-      const int op = cw + A2_COPY_WARPS * lane;      // gather of a 128-row tile pair: tile op >> 6 (K, V or
-      const bool has_op = op < 128;                    // Q0, Q1), 64-column block (op >> 5) & 1, rows 4 (op & 31) ..
-      const int ogrp = op >> 6, oblk = (op >> 5) & 1, orow = (op & 31) * 4;
-      if (has_op) {
-        const int off = ogrp ? rows0 : 0, nr = ogrp ? qrows - rows0 : rows0;
+      // warp 10, 11: the two 64-column blocks of the K tiles (and of group 0's Q tile); warps 12, 13: those of
+      // the V tiles (and of group 1's Q tile).  A lane owns rows 4 lane .. 4 lane + 3 of a tile.
+      const int kind = (warp - 10) >> 1, oblk = (warp - 10) & 1, orow = lane * 4;
+      const bool announces = oblk == 0 && lane == 0;
+      {
+        const int off = kind ? rows0 : 0, nr = kind ? qrows - rows0 : rows0;
         int r[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)      // slots past the group repeat its first row
           r[j] = h * q_head_step + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)] * q_row_step;
-        if ((op & 63) == 0) mbar_arrive_expect_tx(bars + B_FULLQ + ogrp, AT_TILE);
-        tma_gather4(base + ogrp * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
-                    bars + B_FULLQ + ogrp);
+        if (announces) mbar_arrive_expect_tx(bars + B_FULLQ + kind, AT_TILE);
+        tma_gather4(base + kind * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
+                    bars + B_FULLQ + kind);
       }
+      const CUtensorMap* map1 = kind ? &maps.v1 : &maps.k1;
+      const CUtensorMap* map32 = kind ? &maps.v32 : &maps.k32;
+      const CUtensorMap* map64 = kind ? &maps.v64 : &maps.k64;
+      long long cprev = PROF_NOW();
+      int cursor = 0;
       for (int t = 0; t < ntiles; ++t) {
         const uint32_t g = g0 + t, slot = g & 1u, par = (g >> 1) & 1u;
-        int r[4] = {0, 0, 0, 0};
-        if (has_op) {
-          const int lo = t < A2_MAX_TILES ? sTileRun[t] : 0;
-          const int hi = t + 1 <= A2_MAX_TILES ? sTileRun[t + 1] : nruns - 1;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int p = t * KT + orow + j;
-            int row = 0;                     // slots past the union read a real row; their scores are masked
-            if (p < kvlen) {
-              const int ru = run_of(p, lo, hi);
-              row = sRunStart[ru] + p - sRunCum[ru];
-            }
-            r[j] = h * N + row;
-          }
-        }
-        // every copy warp waits for both slots (in order, so its phase view stays exact), then issues
-        if (!mbar_wait(bars + B_FREEK + slot, par, abort_flag)) break;
-        if (!mbar_wait(bars + B_FREEV + slot, par, abort_flag)) break;
-        if (has_op) {
-          uint64_t* full = bars + (ogrp ? B_FULLV : B_FULLK) + slot;
-          if ((op & 63) == 0) mbar_arrive_expect_tx(full, AT_TILE);
-          tma_gather4(base + A2_OFF_SLOT + slot * A2_SLOT + ogrp * AT_TILE + oblk * (KT * 128) + orow * 128,
-                      ogrp ? &mapV : &mapK, oblk * 64, r[0], r[1], r[2], r[3], full);
-        }
+        int r[4];
+        const bool whole = union_rows(sRunStart, sRunCum, nruns, kvlen, t * KT + orow, h * N, cursor, r);
+        const long long c0 = PROF_NOW();
+        if (!mbar_wait(bars + (kind ? B_FREEV : B_FREEK) + slot, par, abort_flag)) break;
+        const long long c1 = PROF_NOW();
+        uint64_t* full = bars + (kind ? B_FULLV : B_FULLK) + slot;
+        if (announces) mbar_arrive_expect_tx(full, AT_TILE);
+        fetch_block(base + A2_OFF_SLOT + slot * A2_SLOT + kind * AT_TILE + oblk * (KT * 128), map1, map32, map64,
+                    oblk * 64, r, whole, lane, full);
+        __syncwarp();
+        const long long c2 = PROF_NOW();
+        if (oblk == 0 && lane == 0) { PROF_ADD(12 + kind * 4, c1 - c0); PROF_ADD(13 + kind * 4, c2 - c1); PROF_ADD(14 + kind * 4, c0 - cprev); PROF_ADD(15 + kind * 4, 1); }
+        cprev = c2;
       }
     } else if (warp == 8) {
       // ================= MMA warp: one lane issues everything, group 0 then group 1 ===============
@@ -824,11 +628,14 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
           const uint32_t tg = g0 + t, slot = tg & 1u;
           const bool more = t + 1 < ntiles;
           const uint32_t v0 = slot ? vlo[1] : vlo[0];
+          const long long m0 = PROF_NOW();
           if (!mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) break;
-          if (more && !mbar_wait(bars + B_FULLK + (slot ^ 1u), ((tg + 1) >> 1) & 1u, abort_flag)) break;
+          PROF_ADD(8, PROF_NOW() - m0); PROF_ADD(11, 1);
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
+            const long long m1 = PROF_NOW();
             if (!mbar_wait(bars + B_P + g, phP[g], abort_flag)) { ok = false; break; }    // P_g is in tensor memory
+            PROF_ADD(9 + g, PROF_NOW() - m1);
             phP[g] ^= 1u;
             tc_fence_after();
             const uint32_t tS = tmem + g * 256, tO = tS + 128;
@@ -837,7 +644,15 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
               umma_ts_lo(tO, tS + s8 * 8, v0 + s8 * (2048 >> 4), dhi, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
             umma_commit(bars + B_O + g);
             if (g == 1) umma_commit(bars + B_FREEV + slot);
-            if (more) mma_qk(g, slot ^ 1u);
+            if (more) {
+              if (g == 0) {      // the next K tile is first needed here
+                const long long m2 = PROF_NOW();
+                if (!mbar_wait(bars + B_FULLK + (slot ^ 1u), ((tg + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
+                PROF_ADD(20, PROF_NOW() - m2);
+                tc_fence_after();
+              }
+              mma_qk(g, slot ^ 1u);
+            }
           }
         }
       }
@@ -854,6 +669,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       rs.l = 0.f;
       bool dead = false;
       for (int t = 0; t < ntiles; ++t) {
+        const long long p0 = PROF_NOW();
         if (!mbar_wait(barS, phS, abort_flag)) { dead = true; break; }
         phS ^= 1u;
         if (t > 0) {      // P V of tile t - 1 finished before Q K^T of tile t: this only tracks the phase
@@ -861,17 +677,25 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
           phO ^= 1u;
         }
         tc_fence_after();
+        const long long p1 = PROF_NOW();
+        long long pm = p1;
         // A warp whose rows all lie past the group's last row skips the arithmetic: its P rows stay
         // whatever S held, which only reaches O rows that are never stored.
         if (warp_has_rows) {
           const int valid = kvlen - t * KT;
-          if (valid >= KT) softmax_tile_2pass<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
-          else softmax_tile_2pass<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          if (valid >= KT) softmax_tile<false, T2T_POLY>(tS_lane, tO_lane, rs, KT, t == 0, sc, &pm);
+          else softmax_tile<true, 0>(tS_lane, tO_lane, rs, valid, t == 0, sc, &pm);
           tmem_wait_st();
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + B_P + grp);
+        if (lane == 0) {
+          mbar_arrive(bars + B_P + grp);
+        }
+        const long long p2 = PROF_NOW();
+        if (gw == 0 && lane == 0 && t > 0) {      // [grp*4 + ..]: wait, pass 1, pass 2, tiles
+          PROF_ADD(grp * 4 + 0, p1 - p0); PROF_ADD(grp * 4 + 1, pm - p1); PROF_ADD(grp * 4 + 2, p2 - pm); PROF_ADD(grp * 4 + 3, 1);
+        }
       }
       if (!dead) {
         if (!mbar_wait(barO, phO, abort_flag)) dead = true;
@@ -916,6 +740,245 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   tc_fence_before();
   __syncthreads();
   if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
+// ---------------------------------------------------------------------------
+// exact attention, tasks of at most QT rows
+// ---------------------------------------------------------------------------
+// The same roles as attn2_kernel with one row group and single K, V and Q buffers, two CTAs to an SM
+// (256 tensor-memory columns and 110 KB of shared memory each) so that one CTA's softmax runs under the
+// other's loads and products:
+//   warps 0..3   softmax, one thread per query row
+//   warp 4       one lane issues every MMA
+//   warp 5, 6    the K tiles (and the task's Q tile) and the V tiles, by TMA: a lane fetches rows 4 lane ..
+//                4 lane + 3 of both 64-column blocks (see fetch_block).  A TMA instruction holds its warp for
+//                about 70 cycles per lane, which threads that also compute cannot afford.
+// Fill g of the K (V) buffer, g counting the tiles this CTA has processed, waits for phase g of freeK (freeV) -
+// phase 0 is completed at start-up, phase g by the commit behind the product that read fill g - 1 - and
+// completes phase g of fullK (fullV).
+constexpr int A1_THREADS = 7 * 32;
+constexpr int A1_OFF_MISC = 3 * AT_TILE;                  // Q, K, V tiles
+constexpr int A1_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
+constexpr int A1_SMEM = A1_OFF_MISC + 256 + A1_SMEM_INTS * 4 + 1024;
+enum { C_S = 0, C_O, C_P, C_FULLK, C_FULLV, C_FREEK, C_FREEV, C_FULLQ, C_COUNT };
+static_assert(2 * (A1_SMEM + 1024) <= 228 * 1024, "two CTAs share an SM");
+
+__global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
+    const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ KVMaps maps,
+    const uint32_t* __restrict__ ub, const int* __restrict__ qperm,
+    __nv_bfloat16* __restrict__ attn_out, float* __restrict__ attn_lse, int* __restrict__ plan, int H, int N, int CQ,
+    int q_row_step, int q_head_step, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* sm = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t sQ = base, sK = base + AT_TILE, sV = base + 2 * AT_TILE;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + A1_OFF_MISC);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + A1_OFF_MISC + C_COUNT * 8);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + A1_OFF_MISC + C_COUNT * 8 + 8);
+  int* sInt = reinterpret_cast<int*>(sm + A1_OFF_MISC + 256);
+  int* sRunStart = sInt;                          // [MAX_RUNS]
+  int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
+  int* sMisc = sRunCum + MAX_RUNS + 8;            // [0] task, [1] runs
+
+  const PlanView pv = plan_view(plan, H, N, CQ);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  if (warp == 0) {
+    tmem_alloc(tmem_slot, 256);
+    tmem_relinquish();
+  }
+  if (tid == 0) {
+    *abort_flag = 0;
+    for (int i = 0; i < C_COUNT; ++i) mbar_init(bars + i, i == C_P ? 4 : 1);
+    mbar_init_fence();
+    mbar_arrive(bars + C_FREEK);      // both buffers start empty
+    mbar_arrive(bars + C_FREEV);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tO = tmem + 128;
+  uint32_t tiles_done = 0, qcnt = 0;      // tiles / non-empty tasks this CTA has processed; every role counts alike
+  uint32_t phS = 0, phO = 0, phP = 0;     // softmax warps: S and O; MMA lane: P
+  const int numTasks = pv.counters[0];
+  const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
+  constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
+  constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
+
+  while (true) {
+    __syncthreads();
+    if (tid == 0) {      // next task of at most QT rows (the two-tile kernel takes the others)
+      int i;
+      do { i = atomicAdd(&pv.counters[1], 1); } while (i < numTasks && pv.tasks[i].w > QT);
+      sMisc[0] = i;
+    }
+    __syncthreads();
+    const int ti = sMisc[0];
+    if (ti >= numTasks || *abort_flag) break;
+    const int4 tk = pv.tasks[ti];
+    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
+    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
+    const size_t rowbase = (size_t)h * N + qs;
+
+    if (kvlen == 0) {   // empty union: O = 0, lse = -inf
+      for (int i = tid; i < qrows * 16; i += A1_THREADS)
+        reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
+      for (int r = tid; r < qrows; r += A1_THREADS) attn_lse[rowbase + r] = -INFINITY;
+      continue;
+    }
+
+    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
+                    pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
+      break;
+    const int nruns = sMisc[1];
+    const int ntiles = cdiv(kvlen, KT);
+    const uint32_t g0 = tiles_done;
+
+    if (warp >= 5) {
+      // ================= copy warps: warp 5 the K tiles (and the task's Q tile), warp 6 the V tiles =========
+      const int kind = warp - 5, orow = lane * 4;
+      if (kind == 0) {      // slots past the task repeat its first row
+        int r[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          r[j] = h * q_head_step + qperm[rowbase + (orow + j < qrows ? orow + j : 0)] * q_row_step;
+        if (lane == 0) mbar_arrive_expect_tx(bars + C_FULLQ, AT_TILE);
+        tma_gather4(sQ + orow * 128, &mapQ, 0, r[0], r[1], r[2], r[3], bars + C_FULLQ);
+        tma_gather4(sQ + KT * 128 + orow * 128, &mapQ, 64, r[0], r[1], r[2], r[3], bars + C_FULLQ);
+      }
+      uint64_t* freeb = bars + (kind ? C_FREEV : C_FREEK);
+      uint64_t* full = bars + (kind ? C_FULLV : C_FULLK);
+      const CUtensorMap* map1 = kind ? &maps.v1 : &maps.k1;
+      const CUtensorMap* map32 = kind ? &maps.v32 : &maps.k32;
+      const CUtensorMap* map64 = kind ? &maps.v64 : &maps.k64;
+      const uint32_t dst = kind ? sV : sK;
+      int cursor = 0;
+      for (int t = 0; t < ntiles; ++t) {
+        const uint32_t g = g0 + t;
+        int r[4];
+        const bool whole = union_rows(sRunStart, sRunCum, nruns, kvlen, t * KT + orow, h * N, cursor, r);
+        if (!mbar_wait(freeb, g & 1u, abort_flag)) break;
+        if (lane == 0) mbar_arrive_expect_tx(full, AT_TILE);
+        fetch_block(dst, map1, map32, map64, 0, r, whole, lane, full);
+        fetch_block(dst + KT * 128, map1, map32, map64, 64, r, whole, lane, full);
+      }
+    } else if (warp == 4) {
+      // ================= MMA warp: one lane issues everything =================
+      if (lane == 0) {
+        constexpr uint32_t dhi = sdesc_hi(1024);
+        const uint32_t qlo = sdesc_lo(sQ, 16), klo = sdesc_lo(sK, 16), vlo = sdesc_lo(sV, KT * 128);
+        auto mma_qk = [&]() {      // S = Q K^T; its completion also frees the K buffer
+#pragma unroll
+          for (int s = 0; s < 8; ++s) {
+            constexpr uint32_t blk = (QT * 128) >> 4;      // second 64-column block of a tile
+            const uint32_t off = (s >> 2) * blk + (s & 3) * 2;
+            umma_ss_lo(tS, qlo + off, klo + off, dhi, idescQK, s > 0 ? 1u : 0u);
+          }
+          umma_commit(bars + C_S);
+          umma_commit(bars + C_FREEK);
+        };
+        tc_fence_after();
+        bool ok = mbar_wait(bars + C_FULLQ, qcnt & 1u, abort_flag) && mbar_wait(bars + C_FULLK, g0 & 1u, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          mma_qk();
+        }
+        for (int t = 0; t < ntiles && ok; ++t) {
+          const uint32_t tg = g0 + t;
+          const bool more = t + 1 < ntiles;
+          if (!mbar_wait(bars + C_FULLV, tg & 1u, abort_flag)) break;
+          if (!mbar_wait(bars + C_P, phP, abort_flag)) break;      // P is in tensor memory
+          phP ^= 1u;
+          tc_fence_after();
+#pragma unroll
+          for (int s8 = 0; s8 < 8; ++s8)
+            umma_ts_lo(tO, tS + s8 * 8, vlo + s8 * (2048 >> 4), dhi, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+          umma_commit(bars + C_O);
+          umma_commit(bars + C_FREEV);
+          if (more) {
+            if (!mbar_wait(bars + C_FULLK, (tg + 1) & 1u, abort_flag)) break;
+            tc_fence_after();
+            mma_qk();
+          }
+        }
+      }
+    } else {
+      // ================= softmax warps: one query row per thread =================
+      const bool warp_has_rows = warp * 32 < qrows;
+      const uint32_t tS_lane = tmem_addr(tS, warp * 32, 0), tO_lane = tmem_addr(tO, warp * 32, 0);
+      RowState rs;
+      rs.m = -INFINITY;
+      rs.l = 0.f;
+      bool dead = false;
+      for (int t = 0; t < ntiles; ++t) {
+        if (!mbar_wait(bars + C_S, phS, abort_flag)) { dead = true; break; }
+        phS ^= 1u;
+        if (t > 0) {      // P V of tile t - 1 finished before Q K^T of tile t: this only tracks the phase
+          if (!mbar_wait(bars + C_O, phO, abort_flag)) { dead = true; break; }
+          phO ^= 1u;
+        }
+        tc_fence_after();
+        // A warp whose rows all lie past the task's last row skips the arithmetic: its P rows stay whatever S
+        // held, which only reaches O rows that are never stored.
+        if (warp_has_rows) {
+          const int valid = kvlen - t * KT;
+          if (valid >= KT) softmax_tile<false, T2T_POLY>(tS_lane, tO_lane, rs, KT, t == 0, sc);
+          else softmax_tile<true, 0>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bars + C_P);
+      }
+      if (!dead) {
+        if (!mbar_wait(bars + C_O, phO, abort_flag)) dead = true;
+        else phO ^= 1u;
+      }
+      if (!dead) {
+        tc_fence_after();
+        if (warp_has_rows) {
+          const float inv = 1.0f / rs.l;
+          const bool wr = tid < qrows;
+          uint4* dst = reinterpret_cast<uint4*>(attn_out + (rowbase + tid) * kD);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            uint32_t v[32];
+            tmem_ld32(tO_lane + c * 32, v);
+            tmem_wait_ld();
+            if (wr) {
+#pragma unroll
+              for (int g = 0; g < 4; ++g) {
+                uint4 o;
+                o.x = pack_bf2(__uint_as_float(v[8 * g + 0]) * inv, __uint_as_float(v[8 * g + 1]) * inv);
+                o.y = pack_bf2(__uint_as_float(v[8 * g + 2]) * inv, __uint_as_float(v[8 * g + 3]) * inv);
+                o.z = pack_bf2(__uint_as_float(v[8 * g + 4]) * inv, __uint_as_float(v[8 * g + 5]) * inv);
+                o.w = pack_bf2(__uint_as_float(v[8 * g + 6]) * inv, __uint_as_float(v[8 * g + 7]) * inv);
+                dst[c * 4 + g] = o;
+              }
+            }
+          }
+          if (wr) attn_lse[rowbase + tid] = (rs.m + log2f(rs.l)) * 0.6931471805599453f;
+        }
+        tc_fence_before();
+      }
+    }
+    tiles_done += ntiles;
+    ++qcnt;
+  }
+  if (*abort_flag) {
+    if (tid == 0 && status) atomicCAS(status, ST_OK, ST_WAIT_TIMEOUT);
+    // a wait gave up: let tile copies still in flight land before the shared memory is released
+    for (int i = 0; i < 100; ++i) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 256);
+  // This kernel may have started while the kernel launched before it (the tasks above QT rows) was still
+  // running.  No CTA leaves before that grid has completed and its results are visible, so that this grid's
+  // completion, which later work in the stream waits for, implies the other's.  (Without a programmatic
+  // launch the instruction returns at once.)
+  asm volatile("griddepcontrol.wait;\n" ::: "memory");
 }
 
 // ---------------------------------------------------------------------------
@@ -1248,7 +1311,7 @@ const DeviceFacts* device_facts() {
   if (!f->ready) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return nullptr;
-    if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AT_SMEM) != cudaSuccess ||
+    if (cudaFuncSetAttribute(attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A1_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(attn2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A2_SMEM) != cudaSuccess ||
         cudaFuncSetAttribute(tail_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TL_SMEM) != cudaSuccess)
       return nullptr;
@@ -1268,7 +1331,7 @@ struct MapSlot {
 };
 std::mutex g_map_mutex;
 bool cached_row_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows) {
-  static MapSlot slots[16] = {};
+  static MapSlot slots[32] = {};
   static unsigned next = 0;
   std::lock_guard<std::mutex> lock(g_map_mutex);
   for (const MapSlot& s : slots)
@@ -1278,7 +1341,7 @@ bool cached_row_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t 
   fresh.rows = rows;
   fresh.box_rows = box_rows;
   if (!make_row_tile_map(&fresh.map, base, rows, box_rows)) return false;
-  slots[next++ % 16] = fresh;
+  slots[next++ % 32] = fresh;
   *out = fresh.map;
   return true;
 }
@@ -1335,12 +1398,16 @@ extern "C" int t2t_tile_attn_exact_strided(const void* q, long long q_row_stride
   if (!facts) return T2T_ERR_CUDA;
   const int sms = facts->sms;
   // tensor maps over q, kp, vp as [H * N, 128] matrices: the kernel fetches tile rows four at a time
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq;
+  KVMaps kv;
   const uint64_t rows = (uint64_t)H * (uint64_t)N;
-  if (!cached_row_map(&mq, q, q_rows, 1) || !cached_row_map(&mk, kp, rows, 1) || !cached_row_map(&mv, vp, rows, 1))
+  if (!cached_row_map(&mq, q, q_rows, 1) || !cached_row_map(&kv.k1, kp, rows, 1) ||
+      !cached_row_map(&kv.k32, kp, rows, 32) || !cached_row_map(&kv.k64, kp, rows, 64) ||
+      !cached_row_map(&kv.v1, vp, rows, 1) || !cached_row_map(&kv.v32, vp, rows, 32) ||
+      !cached_row_map(&kv.v64, vp, rows, 64))
     return T2T_ERR_CUDA;
   // tasks above 128 rows first (one CTA per SM, two row tiles per K/V stream), then the others
-  attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out,
+  attn2_kernel<<<sms, A2_THREADS, A2_SMEM, st>>>(mq, kv, (const uint32_t*)unip, (const int*)qperm, attn_out,
                                                  attn_lse, plan, H, N, CQ, q_row_step, q_head_step, d_status);
   // The two kernels take disjoint tasks (own cursors, own output rows), so the second may start while the
   // first drains: it is launched with programmatic stream serialization and the first kernel releases its
@@ -1348,15 +1415,15 @@ extern "C" int t2t_tile_attn_exact_strided(const void* q, long long q_row_stride
   // as the first kernel's CTAs run out of tasks and exit.  Later work in the stream waits for both as usual.
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * sms);
-  cfg.blockDim = dim3(128);
-  cfg.dynamicSmemBytes = AT_SMEM;
+  cfg.blockDim = dim3(A1_THREADS);
+  cfg.dynamicSmemBytes = A1_SMEM;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, attn_kernel, mq, mk, mv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
+  if (cudaLaunchKernelEx(&cfg, attn_kernel, mq, kv, (const uint32_t*)unip, (const int*)qperm, attn_out, attn_lse,
                          plan, H, N, CQ, q_row_step, q_head_step, d_status) != cudaSuccess)
     return T2T_ERR_CUDA;
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
@@ -1413,3 +1480,14 @@ extern "C" int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, in
   plan_info_kernel<<<1, 32, 0, st>>>(pv.counters, d_info);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
+
+#ifdef T2T_PROF
+extern "C" int t2t_debug_prof(unsigned long long* host_out, int reset) {
+  if (cudaMemcpyFromSymbol(host_out, t2t::g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
+  if (reset) {
+    unsigned long long z[32] = {};
+    if (cudaMemcpyToSymbol(t2t::g_prof, z, sizeof(z)) != cudaSuccess) return 1;
+  }
+  return 0;
+}
+#endif
