@@ -290,18 +290,6 @@ __device__ __forceinline__ bool build_runs(const int* __restrict__ koh, const ui
   return *abort_flag == 0;
 }
 
-#ifdef T2T_PROF
-__device__ unsigned long long g_prof[32];
-__device__ long long g_prof_mid;
-#define PROF_NOW() clock64()
-#define PROF_ADD(i, v) atomicAdd(&g_prof[i], (unsigned long long)(v))
-#else
-#define PROF_NOW() 0ll
-#define PROF_ADD(i, v) do { } while (0)
-#endif
-#ifndef T2T_POLY
-#define T2T_POLY 0
-#endif
 constexpr int AT_TILE = KT * kD * 2;   // 32 KB: one 128-row tile of q, kp or vp
 
 // kp / vp rows (all heads: `row0` is the head's first row) of union positions p0 .. p0 + 3, from the run list of
@@ -391,39 +379,78 @@ __device__ __forceinline__ void fetch_block(uint32_t dst, const CUtensorMap* map
 // fullQ[g].  Ring slot s holds tile g with g & 1 == s, where g counts the tiles this
 // CTA has processed; the n-th fill of a slot waits for phase n of its free barrier
 // (phase 0 is completed at start-up) and completes phase n of its full barrier.
-// 2^x for x <= 8 without the special-function unit: round x to the nearest integer n (the magic-number add
-// leaves n in the low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, well inside a
-// bf16 rounding step), and n added to the exponent field.  Inputs below -125 count as -125 (2^-125 ~ 0).
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -125.0f);
-  const float t = x + 12582912.0f;      // 1.5 * 2^23
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(0.055171408f, f, 0.24261075f);
-  p = fmaf(p, f, 0.69326097f);
-  p = fmaf(p, f, 0.99992812f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+// Packed fp32 pairs (one instruction for two values) and the three-input maximum keep the instruction count of
+// the softmax rows down: the MMA lane and the copy warps share their schedulers.
+__device__ __forceinline__ unsigned long long pack_f2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ unsigned long long add_f2(unsigned long long a, unsigned long long b) {
+  unsigned long long r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// 2^y for two values y <= 8 without the special-function unit: round y to the nearest integer n (the
+// magic-number add leaves n in the low mantissa bits), a cubic for 2^(y - n) on [-0.5, 0.5] (relative error
+// 7.5e-5, well inside a bf16 rounding step), and n added to the exponent field.  Inputs below -125 count as
+// -125 (2^-125 ~ 0).
+__device__ __forceinline__ void exp2_fma2(float y0, float y1, float& p0, float& p1) {
+  const unsigned long long y = pack_f2(fmaxf(y0, -125.0f), fmaxf(y1, -125.0f));
+  const unsigned long long t = add_f2(y, pack_f2(12582912.0f, 12582912.0f));      // 1.5 * 2^23
+  const unsigned long long n = add_f2(t, pack_f2(-12582912.0f, -12582912.0f));
+  const unsigned long long f = fma_f2(n, pack_f2(-1.0f, -1.0f), y);
+  unsigned long long p = fma_f2(pack_f2(0.055171408f, 0.055171408f), f, pack_f2(0.24261075f, 0.24261075f));
+  p = fma_f2(p, f, pack_f2(0.69326097f, 0.69326097f));
+  p = fma_f2(p, f, pack_f2(0.99992812f, 0.99992812f));
+  float q0, q1, t0, t1;
+  unpack_f2(p, q0, q1);
+  unpack_f2(t, t0, t1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
 }
 
 // Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so that few
 // registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16 over the columns S
 // occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always columns that were read
-// before).  One exponential in POLY (0: none) runs on the FMA pipe instead of the special-function unit, whose
-// 16 results per cycle and SM are what bounds two row groups that compute at the same time.  MASK: columns
-// >= valid lie past the union and count as -inf.
-template <bool MASK, int POLY>
+// before).  Two row groups that compute at the same time are bound by the special-function unit (16
+// exponentials per cycle and SM), so every third pair of a full tile takes the FMA-pipe route instead.
+// MASK: columns >= valid lie past the union and count as -inf (all of them through the special-function
+// unit, whose result for -inf is an exact zero).
+constexpr int kFmaPairEvery = 3;
+template <bool MASK>
 __device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid, bool first,
-                                             float sc, long long* prof_mid = nullptr) {
+                                             float sc) {
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t v[32];
     tmem_ld32(tS_lane + c * 32, v);
     tmem_wait_ld();
+    if (MASK) {
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float x = __uint_as_float(v[j]);
-      if (MASK && c * 32 + j >= valid) x = -INFINITY;
-      mx4[j & 3] = fmaxf(mx4[j & 3], x);
+      for (int j = 0; j < 32; ++j)
+        if (c * 32 + j >= valid) v[j] = 0xff800000u;      // -inf
+    }
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      mx4[0] = max3(mx4[0], __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
+      mx4[1] = max3(mx4[1], __uint_as_float(v[j + 2]), __uint_as_float(v[j + 3]));
+      mx4[2] = max3(mx4[2], __uint_as_float(v[j + 4]), __uint_as_float(v[j + 5]));
+      mx4[3] = max3(mx4[3], __uint_as_float(v[j + 6]), __uint_as_float(v[j + 7]));
     }
   }
   const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
@@ -439,33 +466,38 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane,
       rs.m = mnew;
     }
   }
-  const float nm = -rs.m;
-#ifdef T2T_PROF
-  if (prof_mid) *prof_mid = clock64();
-#endif
-  float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+  const unsigned long long sc2 = pack_f2(sc, sc), nm2 = pack_f2(-rs.m, -rs.m);
+  unsigned long long ls2[2] = {0ull, 0ull};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     uint32_t v[32];
     tmem_ld32(tS_lane + c * 32, v);
     tmem_wait_ld();
+    if (MASK) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (c * 32 + j >= valid) v[j] = 0xff800000u;
+    }
     uint32_t pk[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
-      float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-      if (MASK) {
-        if (c * 32 + 2 * j >= valid) x0 = -INFINITY;
-        if (c * 32 + 2 * j + 1 >= valid) x1 = -INFINITY;
+      float y0, y1, p0, p1;
+      unpack_f2(fma_f2(pack_f2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), sc2, nm2), y0, y1);
+      if (!MASK && j % kFmaPairEvery == kFmaPairEvery - 1) {
+        exp2_fma2(y0, y1, p0, p1);
+      } else {
+        p0 = ex2_approx(y0);
+        p1 = ex2_approx(y1);
       }
-      const float y0 = fmaf(x0, sc, nm), y1 = fmaf(x1, sc, nm);
-      const float p0 = (POLY > 0 && (2 * j) % POLY == POLY - 1) ? exp2_fma(y0) : ex2_approx(y0);
-      const float p1 = (POLY > 0 && (2 * j + 1) % POLY == POLY - 1) ? exp2_fma(y1) : ex2_approx(y1);
-      ls4[j & 3] += p0 + p1;
+      ls2[j & 1] = add_f2(ls2[j & 1], pack_f2(p0, p1));
       pk[j] = pack_bf2(p0, p1);
     }
     tmem_st16(tS_lane + c * 16, pk);
   }
-  rs.l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+  float s0, s1, s2, s3;
+  unpack_f2(ls2[0], s0, s1);
+  unpack_f2(ls2[1], s2, s3);
+  rs.l += (s0 + s1) + (s2 + s3);
 }
 
 constexpr int A2_COPY_WARPS = 6;
@@ -574,23 +606,16 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       const CUtensorMap* map1 = kind ? &maps.v1 : &maps.k1;
       const CUtensorMap* map32 = kind ? &maps.v32 : &maps.k32;
       const CUtensorMap* map64 = kind ? &maps.v64 : &maps.k64;
-      long long cprev = PROF_NOW();
       int cursor = 0;
       for (int t = 0; t < ntiles; ++t) {
         const uint32_t g = g0 + t, slot = g & 1u, par = (g >> 1) & 1u;
         int r[4];
         const bool whole = union_rows(sRunStart, sRunCum, nruns, kvlen, t * KT + orow, h * N, cursor, r);
-        const long long c0 = PROF_NOW();
         if (!mbar_wait(bars + (kind ? B_FREEV : B_FREEK) + slot, par, abort_flag)) break;
-        const long long c1 = PROF_NOW();
         uint64_t* full = bars + (kind ? B_FULLV : B_FULLK) + slot;
         if (announces) mbar_arrive_expect_tx(full, AT_TILE);
         fetch_block(base + A2_OFF_SLOT + slot * A2_SLOT + kind * AT_TILE + oblk * (KT * 128), map1, map32, map64,
                     oblk * 64, r, whole, lane, full);
-        __syncwarp();
-        const long long c2 = PROF_NOW();
-        if (oblk == 0 && lane == 0) { PROF_ADD(12 + kind * 4, c1 - c0); PROF_ADD(13 + kind * 4, c2 - c1); PROF_ADD(14 + kind * 4, c0 - cprev); PROF_ADD(15 + kind * 4, 1); }
-        cprev = c2;
       }
     } else if (warp == 8) {
       // ================= MMA warp: one lane issues everything, group 0 then group 1 ===============
@@ -628,14 +653,10 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
           const uint32_t tg = g0 + t, slot = tg & 1u;
           const bool more = t + 1 < ntiles;
           const uint32_t v0 = slot ? vlo[1] : vlo[0];
-          const long long m0 = PROF_NOW();
           if (!mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) break;
-          PROF_ADD(8, PROF_NOW() - m0); PROF_ADD(11, 1);
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
-            const long long m1 = PROF_NOW();
             if (!mbar_wait(bars + B_P + g, phP[g], abort_flag)) { ok = false; break; }    // P_g is in tensor memory
-            PROF_ADD(9 + g, PROF_NOW() - m1);
             phP[g] ^= 1u;
             tc_fence_after();
             const uint32_t tS = tmem + g * 256, tO = tS + 128;
@@ -646,9 +667,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
             if (g == 1) umma_commit(bars + B_FREEV + slot);
             if (more) {
               if (g == 0) {      // the next K tile is first needed here
-                const long long m2 = PROF_NOW();
                 if (!mbar_wait(bars + B_FULLK + (slot ^ 1u), ((tg + 1) >> 1) & 1u, abort_flag)) { ok = false; break; }
-                PROF_ADD(20, PROF_NOW() - m2);
                 tc_fence_after();
               }
               mma_qk(g, slot ^ 1u);
@@ -669,7 +688,6 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       rs.l = 0.f;
       bool dead = false;
       for (int t = 0; t < ntiles; ++t) {
-        const long long p0 = PROF_NOW();
         if (!mbar_wait(barS, phS, abort_flag)) { dead = true; break; }
         phS ^= 1u;
         if (t > 0) {      // P V of tile t - 1 finished before Q K^T of tile t: this only tracks the phase
@@ -677,14 +695,12 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
           phO ^= 1u;
         }
         tc_fence_after();
-        const long long p1 = PROF_NOW();
-        long long pm = p1;
         // A warp whose rows all lie past the group's last row skips the arithmetic: its P rows stay
         // whatever S held, which only reaches O rows that are never stored.
         if (warp_has_rows) {
           const int valid = kvlen - t * KT;
-          if (valid >= KT) softmax_tile<false, T2T_POLY>(tS_lane, tO_lane, rs, KT, t == 0, sc, &pm);
-          else softmax_tile<true, 0>(tS_lane, tO_lane, rs, valid, t == 0, sc, &pm);
+          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
+          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
           tmem_wait_st();
         }
         tc_fence_before();
@@ -692,9 +708,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
         if (lane == 0) {
           mbar_arrive(bars + B_P + grp);
         }
-        const long long p2 = PROF_NOW();
         if (gw == 0 && lane == 0 && t > 0) {      // [grp*4 + ..]: wait, pass 1, pass 2, tiles
-          PROF_ADD(grp * 4 + 0, p1 - p0); PROF_ADD(grp * 4 + 1, pm - p1); PROF_ADD(grp * 4 + 2, p2 - pm); PROF_ADD(grp * 4 + 3, 1);
         }
       }
       if (!dead) {
@@ -923,8 +937,8 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
         // held, which only reaches O rows that are never stored.
         if (warp_has_rows) {
           const int valid = kvlen - t * KT;
-          if (valid >= KT) softmax_tile<false, T2T_POLY>(tS_lane, tO_lane, rs, KT, t == 0, sc);
-          else softmax_tile<true, 0>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
+          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
           tmem_wait_st();
         }
         tc_fence_before();
@@ -1212,16 +1226,27 @@ __global__ void __launch_bounds__(TL_THREADS, 2) tail_kernel(
         m = mnew;
       }
       const float nm = (m == -INFINITY) ? 0.f : -m;
+      const unsigned long long l2e2 = pack_f2(LOG2E, LOG2E), nm2 = pack_f2(nm, nm);
       const float4* cnt4 = reinterpret_cast<const float4*>(sCnt + i * TL_H);
       float ps4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t pk[TL_H / 2];
 #pragma unroll
       for (int k = 0; k < TL_H / 4; ++k) {
         const float4 cn = cnt4[k];
-        const float p0 = ex2_approx(fmaf(s[4 * k], LOG2E, nm));
-        const float p1 = ex2_approx(fmaf(s[4 * k + 1], LOG2E, nm));
-        const float p2 = ex2_approx(fmaf(s[4 * k + 2], LOG2E, nm));
-        const float p3 = ex2_approx(fmaf(s[4 * k + 3], LOG2E, nm));
+        float y0, y1, y2, y3, p0, p1, p2, p3;
+        unpack_f2(fma_f2(pack_f2(s[4 * k], s[4 * k + 1]), l2e2, nm2), y0, y1);
+        unpack_f2(fma_f2(pack_f2(s[4 * k + 2], s[4 * k + 3]), l2e2, nm2), y2, y3);
+        // every third group of four on the FMA pipe: the two CTAs of an SM share one special-function unit.
+        // (A member of the row's union, -inf here, then weighs 2^-125 instead of an exact zero.)
+        if (k % 3 == 2) {
+          exp2_fma2(y0, y1, p0, p1);
+          exp2_fma2(y2, y3, p2, p3);
+        } else {
+          p0 = ex2_approx(y0);
+          p1 = ex2_approx(y1);
+          p2 = ex2_approx(y2);
+          p3 = ex2_approx(y3);
+        }
         ps4[k & 3] = fmaf(p1, cn.y, fmaf(p0, cn.x, ps4[k & 3]));
         ps4[(k + 2) & 3] = fmaf(p3, cn.w, fmaf(p2, cn.z, ps4[(k + 2) & 3]));
         pk[2 * k] = pack_bf2(p0, p1);
@@ -1480,14 +1505,3 @@ extern "C" int t2t_tile_attn_plan_info(const int* plan, int H, int N, int CQ, in
   plan_info_kernel<<<1, 32, 0, st>>>(pv.counters, d_info);
   return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA;
 }
-
-#ifdef T2T_PROF
-extern "C" int t2t_debug_prof(unsigned long long* host_out, int reset) {
-  if (cudaMemcpyFromSymbol(host_out, t2t::g_prof, sizeof(unsigned long long) * 32) != cudaSuccess) return 1;
-  if (reset) {
-    unsigned long long z[32] = {};
-    if (cudaMemcpyToSymbol(t2t::g_prof, z, sizeof(z)) != cudaSuccess) return 1;
-  }
-  return 0;
-}
-#endif
