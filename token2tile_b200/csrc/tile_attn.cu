@@ -431,9 +431,11 @@ __device__ __forceinline__ void exp2_fma2(float y0, float y1, float& p0, float& 
 // MASK: columns >= valid lie past the union and count as -inf (all of them through the special-function
 // unit, whose result for -inf is an exact zero).
 constexpr int kFmaPairEvery = 3;
-template <bool MASK>
+// `halfway` is called by the whole warp once the first 64 columns of P are written, so that the MMA lane can
+// start on them while the rows work on the rest.
+template <bool MASK, typename Halfway>
 __device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid, bool first,
-                                             float sc) {
+                                             float sc, Halfway&& halfway) {
   float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
@@ -493,6 +495,7 @@ __device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane,
       pk[j] = pack_bf2(p0, p1);
     }
     tmem_st16(tS_lane + c * 16, pk);
+    if (c == 1) halfway();
   }
   float s0, s1, s2, s3;
   unpack_f2(ls2[0], s0, s1);
@@ -507,7 +510,7 @@ constexpr int A2_OFF_SLOT = 2 * AT_TILE;                  // after the two Q til
 constexpr int A2_OFF_MISC = A2_OFF_SLOT + 2 * A2_SLOT;
 constexpr int A2_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
 constexpr int A2_SMEM = A2_OFF_MISC + 256 + A2_SMEM_INTS * 4 + 1024;
-enum { B_S = 0, B_O = 2, B_P = 4, B_FULLK = 6, B_FULLV = 8, B_FREEK = 10, B_FREEV = 12, B_FULLQ = 14, B_COUNT = 16 };
+enum { B_S = 0, B_O = 2, B_P = 4, B_FULLK = 8, B_FULLV = 10, B_FREEK = 12, B_FREEV = 14, B_FULLQ = 16, B_COUNT = 18 };   // P: [group][half]
 
 __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
     const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ KVMaps maps,
@@ -539,7 +542,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   if (tid == 0) {
     *abort_flag = 0;
     for (int i = 0; i < B_COUNT; ++i)
-      mbar_init(bars + i, (i >= B_P && i < B_P + 2) ? 4 : 1);
+      mbar_init(bars + i, (i >= B_P && i < B_P + 4) ? 4 : 1);
     mbar_init_fence();
     // all ring slots start empty: complete phase 0 of the free barriers
     for (int i = B_FREEK; i < B_FREEV + 2; ++i) mbar_arrive(bars + i);
@@ -550,7 +553,6 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   const uint32_t tmem = *tmem_slot;
   uint32_t tiles_done = 0, qcnt = 0;      // tiles / non-empty tasks this CTA has processed; every role counts alike
   uint32_t phS = 0, phO = 0;              // softmax warps: phases of their group's S and O barriers
-  uint32_t phP[2] = {0, 0};               // MMA lane: phases of the P barriers
   const int numTasks = pv.counters[0];
   const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
@@ -656,13 +658,18 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
           if (!mbar_wait(bars + B_FULLV + slot, (tg >> 1) & 1u, abort_flag)) break;
 #pragma unroll
           for (int g = 0; g < 2; ++g) {
-            if (!mbar_wait(bars + B_P + g, phP[g], abort_flag)) { ok = false; break; }    // P_g is in tensor memory
-            phP[g] ^= 1u;
-            tc_fence_after();
             const uint32_t tS = tmem + g * 256, tO = tS + 128;
+            // P_g reaches tensor memory in two halves of 64 keys; every P barrier completes once per tile
+            if (!mbar_wait(bars + B_P + g * 2, tg & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
 #pragma unroll
-            for (int s8 = 0; s8 < 8; ++s8)
+            for (int s8 = 0; s8 < 4; ++s8)
               umma_ts_lo(tO, tS + s8 * 8, v0 + s8 * (2048 >> 4), dhi, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+            if (!mbar_wait(bars + B_P + g * 2 + 1, tg & 1u, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (int s8 = 4; s8 < 8; ++s8)
+              umma_ts_lo(tO, tS + s8 * 8, v0 + s8 * (2048 >> 4), dhi, idescPV, 1u);
             umma_commit(bars + B_O + g);
             if (g == 1) umma_commit(bars + B_FREEV + slot);
             if (more) {
@@ -697,19 +704,23 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
         tc_fence_after();
         // A warp whose rows all lie past the group's last row skips the arithmetic: its P rows stay
         // whatever S held, which only reaches O rows that are never stored.
+        auto halfway = [&]() {      // keys 0 .. 63 of P are in tensor memory
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + B_P + grp * 2);
+        };
         if (warp_has_rows) {
           const int valid = kvlen - t * KT;
-          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
-          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc, halfway);
+          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc, halfway);
           tmem_wait_st();
+        } else {
+          halfway();
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bars + B_P + grp);
-        }
-        if (gw == 0 && lane == 0 && t > 0) {      // [grp*4 + ..]: wait, pass 1, pass 2, tiles
-        }
+        if (lane == 0) mbar_arrive(bars + B_P + grp * 2 + 1);
       }
       if (!dead) {
         if (!mbar_wait(barO, phO, abort_flag)) dead = true;
@@ -774,7 +785,7 @@ constexpr int A1_THREADS = 7 * 32;
 constexpr int A1_OFF_MISC = 3 * AT_TILE;                  // Q, K, V tiles
 constexpr int A1_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
 constexpr int A1_SMEM = A1_OFF_MISC + 256 + A1_SMEM_INTS * 4 + 1024;
-enum { C_S = 0, C_O, C_P, C_FULLK, C_FULLV, C_FREEK, C_FREEV, C_FULLQ, C_COUNT };
+enum { C_S = 0, C_O = 1, C_P = 2, C_FULLK = 4, C_FULLV, C_FREEK, C_FREEV, C_FULLQ, C_COUNT };      // P: [half]
 static_assert(2 * (A1_SMEM + 1024) <= 228 * 1024, "two CTAs share an SM");
 
 __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
@@ -803,7 +814,7 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
   }
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < C_COUNT; ++i) mbar_init(bars + i, i == C_P ? 4 : 1);
+    for (int i = 0; i < C_COUNT; ++i) mbar_init(bars + i, (i == C_P || i == C_P + 1) ? 4 : 1);
     mbar_init_fence();
     mbar_arrive(bars + C_FREEK);      // both buffers start empty
     mbar_arrive(bars + C_FREEV);
@@ -814,7 +825,7 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tO = tmem + 128;
   uint32_t tiles_done = 0, qcnt = 0;      // tiles / non-empty tasks this CTA has processed; every role counts alike
-  uint32_t phS = 0, phO = 0, phP = 0;     // softmax warps: S and O; MMA lane: P
+  uint32_t phS = 0, phO = 0;              // softmax warps: phases of the S and O barriers
   const int numTasks = pv.counters[0];
   const float sc = 0.08838834764831845f * 1.4426950408889634f;   // 1/sqrt(128) * log2(e)
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
@@ -902,12 +913,17 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
           const uint32_t tg = g0 + t;
           const bool more = t + 1 < ntiles;
           if (!mbar_wait(bars + C_FULLV, tg & 1u, abort_flag)) break;
-          if (!mbar_wait(bars + C_P, phP, abort_flag)) break;      // P is in tensor memory
-          phP ^= 1u;
+          // P reaches tensor memory in two halves of 64 keys; both P barriers complete once per tile
+          if (!mbar_wait(bars + C_P, tg & 1u, abort_flag)) break;
           tc_fence_after();
 #pragma unroll
-          for (int s8 = 0; s8 < 8; ++s8)
+          for (int s8 = 0; s8 < 4; ++s8)
             umma_ts_lo(tO, tS + s8 * 8, vlo + s8 * (2048 >> 4), dhi, idescPV, (t > 0 || s8 > 0) ? 1u : 0u);
+          if (!mbar_wait(bars + C_P + 1, tg & 1u, abort_flag)) break;
+          tc_fence_after();
+#pragma unroll
+          for (int s8 = 4; s8 < 8; ++s8)
+            umma_ts_lo(tO, tS + s8 * 8, vlo + s8 * (2048 >> 4), dhi, idescPV, 1u);
           umma_commit(bars + C_O);
           umma_commit(bars + C_FREEV);
           if (more) {
@@ -935,15 +951,23 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
         tc_fence_after();
         // A warp whose rows all lie past the task's last row skips the arithmetic: its P rows stay whatever S
         // held, which only reaches O rows that are never stored.
+        auto halfway = [&]() {      // keys 0 .. 63 of P are in tensor memory
+          tmem_wait_st();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bars + C_P);
+        };
         if (warp_has_rows) {
           const int valid = kvlen - t * KT;
-          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc);
-          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc);
+          if (valid >= KT) softmax_tile<false>(tS_lane, tO_lane, rs, KT, t == 0, sc, halfway);
+          else softmax_tile<true>(tS_lane, tO_lane, rs, valid, t == 0, sc, halfway);
           tmem_wait_st();
+        } else {
+          halfway();
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bars + C_P);
+        if (lane == 0) mbar_arrive(bars + C_P + 1);
       }
       if (!dead) {
         if (!mbar_wait(bars + C_O, phO, abort_flag)) dead = true;
