@@ -324,38 +324,112 @@ struct KVMaps {
   CUtensorMap k1, k32, k64, v1, v32, v64;
 };
 
-// One 64-column block of a 128-row K or V tile, fetched by a whole warp.  Lane g owns destination rows
-// 4 g .. 4 g + 3, whose source rows are r[0..3]; `whole` says that they are four consecutive rows of kp / vp.
-// Groups that follow each other in the source as well form a stretch, and a stretch is fetched with 64-row
-// tile loads, then 32-row tile loads, then four-row gathers for what is left (a tile load moves 2.6x / 1.8x
-// the bytes per cycle of a gather; a swizzled tile may start at any multiple of four rows, the pattern being a
-// function of the shared-memory address).  Groups that straddle two runs of the union are gathered.
-// `dst` is the block's first byte; every instruction counts its bytes on `full`.
-__device__ __forceinline__ void fetch_block(uint32_t dst, const CUtensorMap* map1, const CUtensorMap* map32,
-                                            const CUtensorMap* map64, int col, const int (&r)[4], bool whole,
-                                            int lane, uint64_t* full) {
+// How a warp fetches a 128-row K or V tile.  Lane g owns destination rows 4 g .. 4 g + 3, whose source rows are
+// r[0..3]; `whole` says that they are four consecutive rows of kp / vp.  Groups that follow each other in the
+// source as well form a stretch, and a stretch is fetched with 64-row tile loads, then 32-row tile loads, then
+// four-row gathers for what is left (a tile load moves 2.6x / 1.8x the bytes per cycle of a gather; a swizzled
+// tile may start at any multiple of four rows, the pattern being a function of the shared-memory address).
+// Groups that straddle two runs of the union are gathered.  Returns what this lane issues for each 64-column
+// block: FETCH_NONE (a tile load of a lower lane covers its rows), a gather, or a tile load starting at r[0].
+enum { FETCH_NONE = 0, FETCH_GATHER = 1, FETCH_BOX32 = 2, FETCH_BOX64 = 3 };
+__device__ __forceinline__ int fetch_plan(const int (&r)[4], bool whole, int lane) {
   const int prev = __shfl_up_sync(0xffffffffu, r[0], 1);
   const unsigned wmask = __ballot_sync(0xffffffffu, whole);
   const bool linked = whole && lane > 0 && ((wmask >> (lane - 1)) & 1u) && r[0] == prev + 4;
   const unsigned lmask = __ballot_sync(0xffffffffu, linked);      // bit g: group g continues the stretch of g - 1
+  if (!whole) return FETCH_GATHER;
+  const unsigned upto = 0xffffffffu >> (31 - lane);
+  const int start = 31 - __clz((wmask & ~lmask) & upto);
+  const unsigned above = ~lmask & ~upto;
+  const int end = above ? __ffs(above) - 1 : 32;
+  const int len = end - start, k = lane - start;
+  const int k64 = len & ~15, k32 = k64 + ((len - k64) & ~7);
+  if (k < k64) return (k & 15) == 0 ? FETCH_BOX64 : FETCH_NONE;
+  if (k < k32) return ((k - k64) & 7) == 0 ? FETCH_BOX32 : FETCH_NONE;
+  return FETCH_GATHER;
+}
+// One lane's part of one 64-column block (`dst`: the block's first byte; bytes are counted on `full`).
+__device__ __forceinline__ void fetch_issue(int what, uint32_t dst, const CUtensorMap* map1, const CUtensorMap* map32,
+                                            const CUtensorMap* map64, int col, const int (&r)[4], int lane,
+                                            uint64_t* full) {
   const uint32_t mine = dst + lane * 512;
-  if (whole) {
-    const unsigned upto = 0xffffffffu >> (31 - lane);
-    const int start = 31 - __clz((wmask & ~lmask) & upto);
-    const unsigned above = ~lmask & ~upto;
-    const int end = above ? __ffs(above) - 1 : 32;
-    const int len = end - start, k = lane - start;
-    const int k64 = len & ~15, k32 = k64 + ((len - k64) & ~7);
-    if (k < k64) {
-      if ((k & 15) == 0) tma_load_tile(mine, map64, col, r[0], full);
-      return;
-    }
-    if (k < k32) {
-      if (((k - k64) & 7) == 0) tma_load_tile(mine, map32, col, r[0], full);
-      return;
+  if (what == FETCH_GATHER) tma_gather4(mine, map1, col, r[0], r[1], r[2], r[3], full);
+  else if (what == FETCH_BOX32) tma_load_tile(mine, map32, col, r[0], full);
+  else if (what == FETCH_BOX64) tma_load_tile(mine, map64, col, r[0], full);
+}
+
+// 2^x for x <= 8 without the special-function unit: round x to the nearest integer n (the magic-number add
+// leaves n in the low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, well inside a
+// bf16 rounding step), and n added to the exponent field.  Inputs below -125 count as -125 (2^-125 ~ 0).
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -125.0f);
+  const float t = x + 12582912.0f;      // 1.5 * 2^23
+  const float f = x - (t - 12582912.0f);
+  float p = fmaf(0.055171408f, f, 0.24261075f);
+  p = fmaf(p, f, 0.69326097f);
+  p = fmaf(p, f, 0.99992812f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
+// Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so that few
+// registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16 over the columns S
+// occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always columns that were read
+// before).  One exponential in POLY (0: none) runs on the FMA pipe instead of the special-function unit, whose
+// 16 results per cycle and SM are what bounds two row groups that compute at the same time.  MASK: columns
+// >= valid lie past the union and count as -inf.
+template <bool MASK, int POLY>
+__device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid, bool first,
+                                             float sc) {
+  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tS_lane + c * 32, v);
+    tmem_wait_ld();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      float x = __uint_as_float(v[j]);
+      if (MASK && c * 32 + j >= valid) x = -INFINITY;
+      mx4[j & 3] = fmaxf(mx4[j & 3], x);
     }
   }
-  tma_gather4(mine, map1, col, r[0], r[1], r[2], r[3], full);
+  const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+  if (first) {
+    rs.m = mx;
+  } else {
+    const bool grow = mx > rs.m + kLazy;
+    if (__any_sync(0xffffffffu, grow)) {
+      const float mnew = grow ? mx : rs.m;
+      const float alpha = ex2_approx(rs.m - mnew);
+      rescale_rows(tO_lane, alpha);
+      rs.l *= alpha;
+      rs.m = mnew;
+    }
+  }
+  const float nm = -rs.m;
+  float ls4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t v[32];
+    tmem_ld32(tS_lane + c * 32, v);
+    tmem_wait_ld();
+    uint32_t pk[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
+      if (MASK) {
+        if (c * 32 + 2 * j >= valid) x0 = -INFINITY;
+        if (c * 32 + 2 * j + 1 >= valid) x1 = -INFINITY;
+      }
+      const float y0 = fmaf(x0, sc, nm), y1 = fmaf(x1, sc, nm);
+      const float p0 = (POLY > 0 && (2 * j) % POLY == POLY - 1) ? exp2_fma(y0) : ex2_approx(y0);
+      const float p1 = (POLY > 0 && (2 * j + 1) % POLY == POLY - 1) ? exp2_fma(y1) : ex2_approx(y1);
+      ls4[j & 3] += p0 + p1;
+      pk[j] = pack_bf2(p0, p1);
+    }
+    tmem_st16(tS_lane + c * 16, pk);
+  }
+  rs.l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
 }
 
 // ---------------------------------------------------------------------------
@@ -613,11 +687,12 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
         const uint32_t g = g0 + t, slot = g & 1u, par = (g >> 1) & 1u;
         int r[4];
         const bool whole = union_rows(sRunStart, sRunCum, nruns, kvlen, t * KT + orow, h * N, cursor, r);
+        const int what = fetch_plan(r, whole, lane);
         if (!mbar_wait(bars + (kind ? B_FREEV : B_FREEK) + slot, par, abort_flag)) break;
         uint64_t* full = bars + (kind ? B_FULLV : B_FULLK) + slot;
         if (announces) mbar_arrive_expect_tx(full, AT_TILE);
-        fetch_block(base + A2_OFF_SLOT + slot * A2_SLOT + kind * AT_TILE + oblk * (KT * 128), map1, map32, map64,
-                    oblk * 64, r, whole, lane, full);
+        fetch_issue(what, base + A2_OFF_SLOT + slot * A2_SLOT + kind * AT_TILE + oblk * (KT * 128), map1, map32, map64,
+                    oblk * 64, r, lane, full);
       }
     } else if (warp == 8) {
       // ================= MMA warp: one lane issues everything, group 0 then group 1 ===============
@@ -775,13 +850,13 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
 // other's loads and products:
 //   warps 0..3   softmax, one thread per query row
 //   warp 4       one lane issues every MMA
-//   warp 5, 6    the K tiles (and the task's Q tile) and the V tiles, by TMA: a lane fetches rows 4 lane ..
-//                4 lane + 3 of both 64-column blocks (see fetch_block).  A TMA instruction holds its warp for
-//                about 70 cycles per lane, which threads that also compute cannot afford.
+//   warps 5..7   the K and V tiles (and the task's Q tile) by TMA (see fetch_plan).  A TMA instruction holds
+//                its warp for about 70 cycles per lane, which threads that also compute cannot afford, and
+//                one warp alone would need longer for a K tile than the softmax takes.
 // Fill g of the K (V) buffer, g counting the tiles this CTA has processed, waits for phase g of freeK (freeV) -
 // phase 0 is completed at start-up, phase g by the commit behind the product that read fill g - 1 - and
 // completes phase g of fullK (fullV).
-constexpr int A1_THREADS = 7 * 32;
+constexpr int A1_THREADS = 8 * 32;
 constexpr int A1_OFF_MISC = 3 * AT_TILE;                  // Q, K, V tiles
 constexpr int A1_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
 constexpr int A1_SMEM = A1_OFF_MISC + 256 + A1_SMEM_INTS * 4 + 1024;
@@ -814,7 +889,8 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
   }
   if (tid == 0) {
     *abort_flag = 0;
-    for (int i = 0; i < C_COUNT; ++i) mbar_init(bars + i, (i == C_P || i == C_P + 1) ? 4 : 1);
+    for (int i = 0; i < C_COUNT; ++i)
+      mbar_init(bars + i, (i == C_P || i == C_P + 1) ? 4 : ((i == C_FULLK || i == C_FULLV) ? 3 : 1));
     mbar_init_fence();
     mbar_arrive(bars + C_FREEK);      // both buffers start empty
     mbar_arrive(bars + C_FREEV);
@@ -861,9 +937,12 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
     const uint32_t g0 = tiles_done;
 
     if (warp >= 5) {
-      // ================= copy warps: warp 5 the K tiles (and the task's Q tile), warp 6 the V tiles =========
-      const int kind = warp - 5, orow = lane * 4;
-      if (kind == 0) {      // slots past the task repeat its first row
+      // ================= copy warps =================
+      // K and V tiles hold the same rows, so one fetch plan serves both tiles and both of their 64-column
+      // blocks; the three warps share its instructions (the n-th issuing lane belongs to warp n mod 3), K
+      // first: the next Q K^T waits for it.
+      const int cw = warp - 5, orow = lane * 4;
+      if (cw == 0) {      // the task's Q tile; slots past the task repeat its first row
         int r[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j)
@@ -872,21 +951,24 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
         tma_gather4(sQ + orow * 128, &mapQ, 0, r[0], r[1], r[2], r[3], bars + C_FULLQ);
         tma_gather4(sQ + KT * 128 + orow * 128, &mapQ, 64, r[0], r[1], r[2], r[3], bars + C_FULLQ);
       }
-      uint64_t* freeb = bars + (kind ? C_FREEV : C_FREEK);
-      uint64_t* full = bars + (kind ? C_FULLV : C_FULLK);
-      const CUtensorMap* map1 = kind ? &maps.v1 : &maps.k1;
-      const CUtensorMap* map32 = kind ? &maps.v32 : &maps.k32;
-      const CUtensorMap* map64 = kind ? &maps.v64 : &maps.k64;
-      const uint32_t dst = kind ? sV : sK;
       int cursor = 0;
       for (int t = 0; t < ntiles; ++t) {
         const uint32_t g = g0 + t;
         int r[4];
         const bool whole = union_rows(sRunStart, sRunCum, nruns, kvlen, t * KT + orow, h * N, cursor, r);
-        if (!mbar_wait(freeb, g & 1u, abort_flag)) break;
-        if (lane == 0) mbar_arrive_expect_tx(full, AT_TILE);
-        fetch_block(dst, map1, map32, map64, 0, r, whole, lane, full);
-        fetch_block(dst + KT * 128, map1, map32, map64, 64, r, whole, lane, full);
+        int what = fetch_plan(r, whole, lane);
+        const unsigned issuing = __ballot_sync(0xffffffffu, what != FETCH_NONE);
+        if (__popc(issuing & ((1u << lane) - 1u)) % 3 != cw) what = FETCH_NONE;
+        if (!mbar_wait(bars + C_FREEK, g & 1u, abort_flag)) break;
+        // every copy warp arrives on the full barrier, so that none of them can fall two phases behind the
+        // free barrier it waits on (a warp may have nothing to fetch for a tile)
+        if (lane == 0) { if (cw == 0) mbar_arrive_expect_tx(bars + C_FULLK, AT_TILE); else mbar_arrive(bars + C_FULLK); }
+        fetch_issue(what, sK, &maps.k1, &maps.k32, &maps.k64, 0, r, lane, bars + C_FULLK);
+        fetch_issue(what, sK + KT * 128, &maps.k1, &maps.k32, &maps.k64, 64, r, lane, bars + C_FULLK);
+        if (!mbar_wait(bars + C_FREEV, g & 1u, abort_flag)) break;
+        if (lane == 0) { if (cw == 0) mbar_arrive_expect_tx(bars + C_FULLV, AT_TILE); else mbar_arrive(bars + C_FULLV); }
+        fetch_issue(what, sV, &maps.v1, &maps.v32, &maps.v64, 0, r, lane, bars + C_FULLV);
+        fetch_issue(what, sV + KT * 128, &maps.v1, &maps.v32, &maps.v64, 64, r, lane, bars + C_FULLV);
       }
     } else if (warp == 4) {
       // ================= MMA warp: one lane issues everything =================
