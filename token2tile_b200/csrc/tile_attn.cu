@@ -358,80 +358,6 @@ __device__ __forceinline__ void fetch_issue(int what, uint32_t dst, const CUtens
   else if (what == FETCH_BOX64) tma_load_tile(mine, map64, col, r[0], full);
 }
 
-// 2^x for x <= 8 without the special-function unit: round x to the nearest integer n (the magic-number add
-// leaves n in the low mantissa bits), a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 7.5e-5, well inside a
-// bf16 rounding step), and n added to the exponent field.  Inputs below -125 count as -125 (2^-125 ~ 0).
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -125.0f);
-  const float t = x + 12582912.0f;      // 1.5 * 2^23
-  const float f = x - (t - 12582912.0f);
-  float p = fmaf(0.055171408f, f, 0.24261075f);
-  p = fmaf(p, f, 0.69326097f);
-  p = fmaf(p, f, 0.99992812f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
-}
-
-// Softmax of one 128-column S row held in tensor memory, in two passes of 32-column chunks so that few
-// registers are live: the row maximum first, then P = 2^(s * scale - m) packed to bf16 over the columns S
-// occupied (chunk c of S, columns 32 c .., becomes columns 16 c .. of P: always columns that were read
-// before).  One exponential in POLY (0: none) runs on the FMA pipe instead of the special-function unit, whose
-// 16 results per cycle and SM are what bounds two row groups that compute at the same time.  MASK: columns
-// >= valid lie past the union and count as -inf.
-template <bool MASK, int POLY>
-__device__ __forceinline__ void softmax_tile(uint32_t tS_lane, uint32_t tO_lane, RowState& rs, int valid, bool first,
-                                             float sc) {
-  float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t v[32];
-    tmem_ld32(tS_lane + c * 32, v);
-    tmem_wait_ld();
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      float x = __uint_as_float(v[j]);
-      if (MASK && c * 32 + j >= valid) x = -INFINITY;
-      mx4[j & 3] = fmaxf(mx4[j & 3], x);
-    }
-  }
-  const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
-  if (first) {
-    rs.m = mx;
-  } else {
-    const bool grow = mx > rs.m + kLazy;
-    if (__any_sync(0xffffffffu, grow)) {
-      const float mnew = grow ? mx : rs.m;
-      const float alpha = ex2_approx(rs.m - mnew);
-      rescale_rows(tO_lane, alpha);
-      rs.l *= alpha;
-      rs.m = mnew;
-    }
-  }
-  const float nm = -rs.m;
-  float ls4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t v[32];
-    tmem_ld32(tS_lane + c * 32, v);
-    tmem_wait_ld();
-    uint32_t pk[16];
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float x0 = __uint_as_float(v[2 * j]), x1 = __uint_as_float(v[2 * j + 1]);
-      if (MASK) {
-        if (c * 32 + 2 * j >= valid) x0 = -INFINITY;
-        if (c * 32 + 2 * j + 1 >= valid) x1 = -INFINITY;
-      }
-      const float y0 = fmaf(x0, sc, nm), y1 = fmaf(x1, sc, nm);
-      const float p0 = (POLY > 0 && (2 * j) % POLY == POLY - 1) ? exp2_fma(y0) : ex2_approx(y0);
-      const float p1 = (POLY > 0 && (2 * j + 1) % POLY == POLY - 1) ? exp2_fma(y1) : ex2_approx(y1);
-      ls4[j & 3] += p0 + p1;
-      pk[j] = pack_bf2(p0, p1);
-    }
-    tmem_st16(tS_lane + c * 16, pk);
-  }
-  rs.l += (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-}
-
 // ---------------------------------------------------------------------------
 // exact attention, tasks of QT + 1 .. TASK_ROWS rows
 // ---------------------------------------------------------------------------
