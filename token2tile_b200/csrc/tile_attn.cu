@@ -526,7 +526,7 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   int* sInt = reinterpret_cast<int*>(sm + A2_OFF_MISC + 256);
   int* sRunStart = sInt;                          // [MAX_RUNS]
   int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
-  int* sMisc = sRunCum + MAX_RUNS + 8;            // [0] task, [1] runs; scan scratch from [8]
+  int* sMisc = sRunCum + MAX_RUNS + 8;            // [1] runs; [2..7] the next task: index, head, cluster, first row, rows, union length
 
   const PlanView pv = plan_view(plan, H, N, CQ);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -558,53 +558,64 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
 
+  // The next task of more than QT rows is fetched (cursor, task record, union length: three dependent trips
+  // to global memory) while the current one runs, by a lane that has nothing else to do.
+  auto fetch_task = [&]() {
+    int i;
+    do { i = atomicAdd(&pv.counters[4], 1); } while (i < numTasks && pv.tasks[i].w <= QT);
+    int4 tk = make_int4(0, 0, 0, 0);
+    int len = 0;
+    if (i < numTasks) {
+      tk = pv.tasks[i];
+      len = pv.kv_lens[(size_t)tk.x * CQ + tk.y];
+    }
+    sMisc[2] = i; sMisc[3] = tk.x; sMisc[4] = tk.y; sMisc[5] = tk.z; sMisc[6] = tk.w; sMisc[7] = len;
+  };
+  if (warp == 9 && lane == 0) fetch_task();
+
   while (true) {
     __syncthreads();
-    if (tid == 0) {      // next task of more than QT rows
-      int i;
-      do { i = atomicAdd(&pv.counters[4], 1); } while (i < numTasks && pv.tasks[i].w <= QT);
-      sMisc[0] = i;
-    }
-    __syncthreads();
-    const int ti = sMisc[0];
+    const int ti = sMisc[2], h = sMisc[3], qc = sMisc[4], qs = sMisc[5], qrows = sMisc[6], kvlen = sMisc[7];
+    __syncthreads();      // everyone has the task: the record may be overwritten
     if (ti >= numTasks || *abort_flag) break;
-    const int4 tk = pv.tasks[ti];
-    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
-    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
     const size_t rowbase = (size_t)h * N + qs;
 
     if (kvlen == 0) {   // empty union: O = 0, lse = -inf
+      if (warp == 9 && lane == 0) fetch_task();
       for (int i = tid; i < qrows * 16; i += A2_THREADS)
         reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
       for (int r = tid; r < qrows; r += A2_THREADS) attn_lse[rowbase + r] = -INFINITY;
       continue;
     }
 
+    const int rows0 = (qrows + 1) >> 1;                       // rows of group 0; group 1 takes the rest
+    if (warp >= 10 && warp < 14) {      // the Q tiles need no run list: their gathers go first
+      const int kind = (warp - 10) >> 1, oblk = (warp - 10) & 1, orow = lane * 4;
+      const int off = kind ? rows0 : 0, nr = kind ? qrows - rows0 : rows0;
+      int r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)      // slots past the group repeat its first row
+        r[j] = h * q_head_step + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)] * q_row_step;
+      if (oblk == 0 && lane == 0) mbar_arrive_expect_tx(bars + B_FULLQ + kind, AT_TILE);
+      tma_gather4(base + kind * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
+                  bars + B_FULLQ + kind);
+    }
     // ---- runs of selected, non-empty key clusters ------------------------------------------------
     if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
                     pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
       break;
     const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
-    const int rows0 = (qrows + 1) >> 1;                       // rows of group 0; group 1 takes the rest
     const uint32_t g0 = tiles_done;
 
-    if (warp >= 10 && warp < 14) {
-      // ================= copy warps: Q tiles of both groups, then the K / V stream ===============
-      // warp 10, 11: the two 64-column blocks of the K tiles (and of group 0's Q tile); warps 12, 13: those of
-      // the V tiles (and of group 1's Q tile).  A lane owns rows 4 lane .. 4 lane + 3 of a tile.
+    if (warp == 9) {
+      if (lane == 0) fetch_task();
+    } else if (warp >= 10 && warp < 14) {
+      // ================= copy warps: the K / V stream ===============
+      // warp 10, 11: the two 64-column blocks of the K tiles (above: of group 0's Q tile); warps 12, 13: those
+      // of the V tiles (of group 1's Q tile).  A lane owns rows 4 lane .. 4 lane + 3 of a tile.
       const int kind = (warp - 10) >> 1, oblk = (warp - 10) & 1, orow = lane * 4;
       const bool announces = oblk == 0 && lane == 0;
-      {
-        const int off = kind ? rows0 : 0, nr = kind ? qrows - rows0 : rows0;
-        int r[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)      // slots past the group repeat its first row
-          r[j] = h * q_head_step + qperm[rowbase + off + (orow + j < nr ? orow + j : 0)] * q_row_step;
-        if (announces) mbar_arrive_expect_tx(bars + B_FULLQ + kind, AT_TILE);
-        tma_gather4(base + kind * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
-                    bars + B_FULLQ + kind);
-      }
       const CUtensorMap* map1 = kind ? &maps.v1 : &maps.k1;
       const CUtensorMap* map32 = kind ? &maps.v32 : &maps.k32;
       const CUtensorMap* map64 = kind ? &maps.v64 : &maps.k64;
@@ -804,7 +815,7 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
   int* sInt = reinterpret_cast<int*>(sm + A1_OFF_MISC + 256);
   int* sRunStart = sInt;                          // [MAX_RUNS]
   int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
-  int* sMisc = sRunCum + MAX_RUNS + 8;            // [0] task, [1] runs
+  int* sMisc = sRunCum + MAX_RUNS + 8;            // [1] runs; [2..7] the next task: index, head, cluster, first row, rows, union length
 
   const PlanView pv = plan_view(plan, H, N, CQ);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -833,26 +844,45 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
 
+  // The next task of at most QT rows (the two-tile kernel takes the others) is fetched - cursor, task record,
+  // union length: three dependent trips to global memory - by a copy warp once it has issued the current
+  // task's last tile, while the other roles are still busy with it.
+  auto fetch_task = [&]() {
+    int i;
+    do { i = atomicAdd(&pv.counters[1], 1); } while (i < numTasks && pv.tasks[i].w > QT);
+    int4 tk = make_int4(0, 0, 0, 0);
+    int len = 0;
+    if (i < numTasks) {
+      tk = pv.tasks[i];
+      len = pv.kv_lens[(size_t)tk.x * CQ + tk.y];
+    }
+    sMisc[2] = i; sMisc[3] = tk.x; sMisc[4] = tk.y; sMisc[5] = tk.z; sMisc[6] = tk.w; sMisc[7] = len;
+  };
+  if (warp == 7 && lane == 0) fetch_task();
+
   while (true) {
     __syncthreads();
-    if (tid == 0) {      // next task of at most QT rows (the two-tile kernel takes the others)
-      int i;
-      do { i = atomicAdd(&pv.counters[1], 1); } while (i < numTasks && pv.tasks[i].w > QT);
-      sMisc[0] = i;
-    }
-    __syncthreads();
-    const int ti = sMisc[0];
+    const int ti = sMisc[2], h = sMisc[3], qc = sMisc[4], qs = sMisc[5], qrows = sMisc[6], kvlen = sMisc[7];
+    __syncthreads();      // everyone has the task: the record may be overwritten
     if (ti >= numTasks || *abort_flag) break;
-    const int4 tk = pv.tasks[ti];
-    const int h = tk.x, qc = tk.y, qs = tk.z, qrows = tk.w;
-    const int kvlen = pv.kv_lens[(size_t)h * CQ + qc];
     const size_t rowbase = (size_t)h * N + qs;
 
     if (kvlen == 0) {   // empty union: O = 0, lse = -inf
+      if (warp == 7 && lane == 0) fetch_task();
       for (int i = tid; i < qrows * 16; i += A1_THREADS)
         reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
       for (int r = tid; r < qrows; r += A1_THREADS) attn_lse[rowbase + r] = -INFINITY;
       continue;
+    }
+    if (warp == 5) {      // the task's Q tile needs no run list: its gathers go first; slots past the task repeat its first row
+      const int orow = lane * 4;
+      int r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        r[j] = h * q_head_step + qperm[rowbase + (orow + j < qrows ? orow + j : 0)] * q_row_step;
+      if (lane == 0) mbar_arrive_expect_tx(bars + C_FULLQ, AT_TILE);
+      tma_gather4(sQ + orow * 128, &mapQ, 0, r[0], r[1], r[2], r[3], bars + C_FULLQ);
+      tma_gather4(sQ + KT * 128 + orow * 128, &mapQ, 64, r[0], r[1], r[2], r[3], bars + C_FULLQ);
     }
 
     if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
@@ -868,15 +898,6 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
       // blocks; the three warps share its instructions (the n-th issuing lane belongs to warp n mod 3), K
       // first: the next Q K^T waits for it.
       const int cw = warp - 5, orow = lane * 4;
-      if (cw == 0) {      // the task's Q tile; slots past the task repeat its first row
-        int r[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-          r[j] = h * q_head_step + qperm[rowbase + (orow + j < qrows ? orow + j : 0)] * q_row_step;
-        if (lane == 0) mbar_arrive_expect_tx(bars + C_FULLQ, AT_TILE);
-        tma_gather4(sQ + orow * 128, &mapQ, 0, r[0], r[1], r[2], r[3], bars + C_FULLQ);
-        tma_gather4(sQ + KT * 128 + orow * 128, &mapQ, 64, r[0], r[1], r[2], r[3], bars + C_FULLQ);
-      }
       int cursor = 0;
       for (int t = 0; t < ntiles; ++t) {
         const uint32_t g = g0 + t;
@@ -896,6 +917,7 @@ __global__ void __launch_bounds__(A1_THREADS, 2) attn_kernel(
         fetch_issue(what, sV, &maps.v1, &maps.v32, &maps.v64, 0, r, lane, bars + C_FULLV);
         fetch_issue(what, sV + KT * 128, &maps.v1, &maps.v32, &maps.v64, 64, r, lane, bars + C_FULLV);
       }
+      if (warp == 7 && lane == 0) fetch_task();
     } else if (warp == 4) {
       // ================= MMA warp: one lane issues everything =================
       if (lane == 0) {
