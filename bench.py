@@ -36,7 +36,7 @@ WORKLOAD = dict(name="wan2.1-14b-720p-self-attention-layer", H=40, grid="720p", 
                 s_frac=0.015)
 KERNELS_REBUILD = 2 + 21 + 3 + 1 + 1 + 3  # project, kmeans (3 assign+fix, 3x3 grouping, 3 means, 3 value stats), centroid moments+select+fix, gather, plan, attention (two kernels) + merge
 KERNELS_REUSE = 1 + 1 + 3 + 3   # project q, gather k, value stats, attention (two kernels) + merge
-ATTN_DRAM_BYTES_480P_8H = 417.5e6      # attn2_kernel (206.6 MB) + attn_kernel (210.9 MB), H 8, N 32,760 (ncu)
+ATTN_DRAM_BYTES_480P_8H = 444.2e6      # attn2_kernel (206.6 MB) + attn_kernel (210.9 MB), H 8, N 32,760 (ncu)
 METRIC = "t2t_attn_ms_per_layer"
 UNIT = "ms/layer"
 
