@@ -242,50 +242,54 @@ __device__ __forceinline__ void rescale_rows(uint32_t tO_lane, float alpha) {
 
 // The union of one task as runs of consecutive kp / vp rows: maximal stretches of selected, non-empty key
 // clusters that follow each other.  sRunStart[r] = first row of run r, sRunCum[r] = position of its first
-// token in the union, sRunCum[runs] = union length, sMisc[1] = runs.  Warp 0 does the work with the bitmap as
-// 64-bit words (two bitmap words per lane): a run starts at a set bit whose lower neighbour is clear and ends
-// at a set bit whose upper neighbour is clear, so the r-th start and the r-th end delimit run r.  Called by
-// every thread of the CTA (it ends with a CTA-wide barrier).  Returns false when the run list would not fit
-// (the abort flag is then set).
+// token in the union, sRunCum[runs] = union length, *runs_out = runs.  One warp does the work with the bitmap
+// as 64-bit words (two bitmap words per lane): a run starts at a set bit whose lower neighbour is clear and
+// ends at a set bit whose upper neighbour is clear, so the r-th start and the r-th end delimit run r.  A run
+// list that would not fit raises the abort flag.
+__device__ __forceinline__ void build_runs_warp(const int* __restrict__ koh, const uint32_t* __restrict__ ubr,
+                                                const uint32_t* __restrict__ nonempty, int* sRunStart, int* sRunCum,
+                                                int* runs_out, volatile int* abort_flag, int* status) {
+  const int lane = threadIdx.x & 31;
+  const unsigned long long sel = ((unsigned long long)(ubr[2 * lane + 1] & nonempty[2 * lane + 1]) << 32) |
+                                 (unsigned long long)(ubr[2 * lane] & nonempty[2 * lane]);
+  // neighbours across the lane boundary
+  const unsigned long long below = __shfl_up_sync(0xffffffffu, sel, 1), above = __shfl_down_sync(0xffffffffu, sel, 1);
+  const unsigned long long carry_in = lane > 0 ? below >> 63 : 0ull;
+  const unsigned long long carry_out = lane < 31 ? (above & 1ull) << 63 : 0ull;
+  unsigned long long starts = sel & ~((sel << 1) | carry_in);
+  unsigned long long ends = sel & ~((sel >> 1) | carry_out);
+  const int mine = __popcll(starts);
+  const int before_s = warp_incl_scan(mine, lane) - mine;
+  const int before_e = warp_incl_scan(__popcll(ends), lane) - __popcll(ends);
+  const int runs = __shfl_sync(0xffffffffu, before_s + mine, 31);
+  if (runs > MAX_RUNS) {      // cannot happen for C = 2048; guard the static arrays anyway
+    if (lane == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
+    return;
+  }
+  int r = before_s;
+  for (; starts; starts &= starts - 1) sRunStart[r++] = koh[64 * lane + __ffsll((long long)starts) - 1];
+  r = before_e;
+  for (; ends; ends &= ends - 1) sRunCum[r++] = koh[64 * lane + __ffsll((long long)ends)];      // one past the run's last row
+  __syncwarp();
+  // lengths -> positions: every lane turns a block of consecutive runs into a running sum
+  const int per = (runs + 31) >> 5, lo = min(lane * per, runs), hi = min(lo + per, runs);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += sRunCum[i] - sRunStart[i];
+  int pos = warp_incl_scan(sum, lane) - sum;
+  const int total = __shfl_sync(0xffffffffu, pos + sum, 31);
+  for (int i = lo; i < hi; ++i) {
+    const int len = sRunCum[i] - sRunStart[i];
+    sRunCum[i] = pos;
+    pos += len;
+  }
+  if (lane == 0) { sRunCum[runs] = total; *runs_out = runs; }
+}
+// The same for a whole CTA: warp 0 builds the list into sMisc[1], a CTA-wide barrier publishes it.  Returns
+// false when the list would not fit (the abort flag is then set).
 __device__ __forceinline__ bool build_runs(const int* __restrict__ koh, const uint32_t* __restrict__ ubr,
                                            const uint32_t* __restrict__ nonempty, int* sRunStart, int* sRunCum,
                                            int* sMisc, volatile int* abort_flag, int* status) {
-  const int lane = threadIdx.x & 31;
-  if ((threadIdx.x >> 5) == 0) {
-    const unsigned long long sel = ((unsigned long long)(ubr[2 * lane + 1] & nonempty[2 * lane + 1]) << 32) |
-                                   (unsigned long long)(ubr[2 * lane] & nonempty[2 * lane]);
-    // neighbours across the lane boundary
-    const unsigned long long below = __shfl_up_sync(0xffffffffu, sel, 1), above = __shfl_down_sync(0xffffffffu, sel, 1);
-    const unsigned long long carry_in = lane > 0 ? below >> 63 : 0ull;
-    const unsigned long long carry_out = lane < 31 ? (above & 1ull) << 63 : 0ull;
-    unsigned long long starts = sel & ~((sel << 1) | carry_in);
-    unsigned long long ends = sel & ~((sel >> 1) | carry_out);
-    const int mine = __popcll(starts);
-    const int before_s = warp_incl_scan(mine, lane) - mine;
-    const int before_e = warp_incl_scan(__popcll(ends), lane) - __popcll(ends);
-    const int runs = __shfl_sync(0xffffffffu, before_s + mine, 31);
-    if (runs > MAX_RUNS) {      // cannot happen for C = 2048; guard the static arrays anyway
-      if (lane == 0) { *abort_flag = 1; if (status) atomicExch(status, ST_BAD_PLAN); }
-    } else {
-      int r = before_s;
-      for (; starts; starts &= starts - 1) sRunStart[r++] = koh[64 * lane + __ffsll((long long)starts) - 1];
-      r = before_e;
-      for (; ends; ends &= ends - 1) sRunCum[r++] = koh[64 * lane + __ffsll((long long)ends)];      // one past the run's last row
-      __syncwarp();
-      // lengths -> positions: every lane turns a block of consecutive runs into a running sum
-      const int per = (runs + 31) >> 5, lo = min(lane * per, runs), hi = min(lo + per, runs);
-      int sum = 0;
-      for (int i = lo; i < hi; ++i) sum += sRunCum[i] - sRunStart[i];
-      int pos = warp_incl_scan(sum, lane) - sum;
-      const int total = __shfl_sync(0xffffffffu, pos + sum, 31);
-      for (int i = lo; i < hi; ++i) {
-        const int len = sRunCum[i] - sRunStart[i];
-        sRunCum[i] = pos;
-        pos += len;
-      }
-      if (lane == 0) { sRunCum[runs] = total; sMisc[1] = runs; }
-    }
-  }
+  if ((threadIdx.x >> 5) == 0) build_runs_warp(koh, ubr, nonempty, sRunStart, sRunCum, sMisc + 1, abort_flag, status);
   __syncthreads();
   return *abort_flag == 0;
 }
@@ -508,7 +512,8 @@ constexpr int A2_THREADS = (10 + A2_COPY_WARPS) * 32;   // 8 softmax warps, the 
 constexpr int A2_SLOT = 2 * AT_TILE;                      // K tile, V tile
 constexpr int A2_OFF_SLOT = 2 * AT_TILE;                  // after the two Q tiles
 constexpr int A2_OFF_MISC = A2_OFF_SLOT + 2 * A2_SLOT;
-constexpr int A2_SMEM_INTS = 2 * MAX_RUNS + 8 + 32;
+constexpr int A2_RUN_INTS = 2 * MAX_RUNS + 8;                // one run list: starts, positions
+constexpr int A2_SMEM_INTS = 2 * A2_RUN_INTS + 32;
 constexpr int A2_SMEM = A2_OFF_MISC + 256 + A2_SMEM_INTS * 4 + 1024;
 enum { B_S = 0, B_O = 2, B_P = 4, B_FULLK = 8, B_FULLV = 10, B_FREEK = 12, B_FREEV = 14, B_FULLQ = 16, B_COUNT = 18 };   // P: [group][half]
 
@@ -524,9 +529,8 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sm + A2_OFF_MISC + B_COUNT * 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(sm + A2_OFF_MISC + B_COUNT * 8 + 8);
   int* sInt = reinterpret_cast<int*>(sm + A2_OFF_MISC + 256);
-  int* sRunStart = sInt;                          // [MAX_RUNS]
-  int* sRunCum = sRunStart + MAX_RUNS;            // [MAX_RUNS + 1]
-  int* sMisc = sRunCum + MAX_RUNS + 8;            // [1] runs; [2..7] the next task: index, head, cluster, first row, rows, union length
+  int* sRuns = sInt;                              // two run lists (this task's, the next one's): [MAX_RUNS] starts, [MAX_RUNS + 1] positions
+  int* sMisc = sInt + 2 * A2_RUN_INTS;            // [2..7] the next task: index, head, cluster, first row, rows, union length; [8], [9] runs of the two lists
 
   const PlanView pv = plan_view(plan, H, N, CQ);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -558,30 +562,47 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
   constexpr uint32_t idescQK = make_idesc_bf16(128, KT, false, false);
   constexpr uint32_t idescPV = make_idesc_bf16(128, kD, false, true);
 
-  // The next task of more than QT rows is fetched (cursor, task record, union length: three dependent trips
-  // to global memory) while the current one runs, by a lane that has nothing else to do.
-  auto fetch_task = [&]() {
-    int i;
-    do { i = atomicAdd(&pv.counters[4], 1); } while (i < numTasks && pv.tasks[i].w <= QT);
-    int4 tk = make_int4(0, 0, 0, 0);
-    int len = 0;
-    if (i < numTasks) {
-      tk = pv.tasks[i];
-      len = pv.kv_lens[(size_t)tk.x * CQ + tk.y];
+  // The next task of more than QT rows is prepared while the current one runs, by warp 9, which has nothing
+  // else to do: cursor, task record and union length (three dependent trips to global memory), then the run
+  // list of its union into the list the current task does not use.
+  auto prepare_task = [&](int list) {
+    int i = 0, th = 0, tc = 0, len = 0;
+    if (lane == 0) {
+      do { i = atomicAdd(&pv.counters[4], 1); } while (i < numTasks && pv.tasks[i].w <= QT);
+      int4 tk = make_int4(0, 0, 0, 0);
+      if (i < numTasks) {
+        tk = pv.tasks[i];
+        len = pv.kv_lens[(size_t)tk.x * CQ + tk.y];
+      }
+      th = tk.x;
+      tc = tk.y;
+      sMisc[2] = i; sMisc[3] = tk.x; sMisc[4] = tk.y; sMisc[5] = tk.z; sMisc[6] = tk.w; sMisc[7] = len;
     }
-    sMisc[2] = i; sMisc[3] = tk.x; sMisc[4] = tk.y; sMisc[5] = tk.z; sMisc[6] = tk.w; sMisc[7] = len;
+    i = __shfl_sync(0xffffffffu, i, 0);
+    th = __shfl_sync(0xffffffffu, th, 0);
+    tc = __shfl_sync(0xffffffffu, tc, 0);
+    len = __shfl_sync(0xffffffffu, len, 0);
+    if (i < numTasks && len > 0)
+      build_runs_warp(pv.k_off + (size_t)th * (kC + 1), ub + ((size_t)th * CQ + tc) * (kC / 32),
+                      pv.nonempty + (size_t)th * (kC / 32), sRuns + list * A2_RUN_INTS,
+                      sRuns + list * A2_RUN_INTS + MAX_RUNS, sMisc + 8 + list, abort_flag, status);
   };
-  if (warp == 9 && lane == 0) fetch_task();
+  int list = 0;      // the run list of the current task
+  if (warp == 9) prepare_task(0);
 
   while (true) {
     __syncthreads();
-    const int ti = sMisc[2], h = sMisc[3], qc = sMisc[4], qs = sMisc[5], qrows = sMisc[6], kvlen = sMisc[7];
+    const int ti = sMisc[2], h = sMisc[3], qs = sMisc[5], qrows = sMisc[6], kvlen = sMisc[7];
     __syncthreads();      // everyone has the task: the record may be overwritten
     if (ti >= numTasks || *abort_flag) break;
     const size_t rowbase = (size_t)h * N + qs;
+    const int* sRunStart = sRuns + list * A2_RUN_INTS;
+    const int* sRunCum = sRunStart + MAX_RUNS;
+    const int nruns = sMisc[8 + list];
+    list ^= 1;
+    if (warp == 9) prepare_task(list);
 
     if (kvlen == 0) {   // empty union: O = 0, lse = -inf
-      if (warp == 9 && lane == 0) fetch_task();
       for (int i = tid; i < qrows * 16; i += A2_THREADS)
         reinterpret_cast<uint4*>(attn_out + (rowbase + (i >> 4)) * kD)[i & 15] = make_uint4(0u, 0u, 0u, 0u);
       for (int r = tid; r < qrows; r += A2_THREADS) attn_lse[rowbase + r] = -INFINITY;
@@ -600,17 +621,10 @@ __global__ void __launch_bounds__(A2_THREADS, 1) attn2_kernel(
       tma_gather4(base + kind * AT_TILE + oblk * (KT * 128) + orow * 128, &mapQ, oblk * 64, r[0], r[1], r[2], r[3],
                   bars + B_FULLQ + kind);
     }
-    // ---- runs of selected, non-empty key clusters ------------------------------------------------
-    if (!build_runs(pv.k_off + (size_t)h * (kC + 1), ub + ((size_t)h * CQ + qc) * (kC / 32),
-                    pv.nonempty + (size_t)h * (kC / 32), sRunStart, sRunCum, sMisc, abort_flag, status))
-      break;
-    const int nruns = sMisc[1];
     const int ntiles = cdiv(kvlen, KT);
     const uint32_t g0 = tiles_done;
 
-    if (warp == 9) {
-      if (lane == 0) fetch_task();
-    } else if (warp >= 10 && warp < 14) {
+    if (warp >= 10 && warp < 14) {
       // ================= copy warps: the K / V stream ===============
       // warp 10, 11: the two 64-column blocks of the K tiles (above: of group 0's Q tile); warps 12, 13: those
       // of the V tiles (of group 1's Q tile).  A lane owns rows 4 lane .. 4 lane + 3 of a tile.
