@@ -319,11 +319,18 @@ def run_ours(args, rank, world, local_rank):
     stages = op.stage_times()
     op.profile = False
     tasks, pairs = op.plan_info()
+    # rows of the query clusters against the 128-row tensor-core tiles their tasks occupy: full 256-row tasks and
+    # remainders above 128 rows take two tiles, remainders of at most 128 rows one
+    sizes = op.last_structure["tile_sizes"].to(torch.int64)
+    rem = sizes % 256
+    row_tiles = 2 * (sizes // 256) + (rem > 128).to(torch.int64) * 2 + ((rem > 0) & (rem <= 128)).to(torch.int64)
+    m_util = float(sizes.sum().item()) / max(1.0, 128.0 * float(row_tiles.sum().item()))
     if args.light:
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world,
                               "config": {"workload": W["name"], "H": W["H"], "N": N, "CQ": CQ},
-                              "stages_ms": stages, "tasks": tasks, "pairs": pairs, "clocks": clocks}))
+                              "stages_ms": stages, "tasks": tasks, "pairs": pairs, "m_utilisation": m_util,
+                              "clocks": clocks}))
         if world > 1:
             dist.destroy_process_group()
         return
@@ -563,7 +570,7 @@ def run_ours(args, rank, world, local_rank):
                     "serial_ms": e2e_serial_ms},
             "gpu_launches": KERNELS_REBUILD * args.steps, "clocks": clocks,
             "reuse_ms": reuse_ms, "amortised_ms_1_rebuild_7_reuse": amort, "stages_ms": stages,
-            "reuse_stages_ms": reuse_stages, "stage_roofline": stage_roof, "tasks": tasks,
+            "reuse_stages_ms": reuse_stages, "stage_roofline": stage_roof, "tasks": tasks, "m_utilisation": m_util,
             "dense_ms": dense, "fastest_dense_ms": dense_best, "budgets": budgets, "init_ms": init_ms,
             "config_480p": config2, "dit_step_ulysses8": dit,
             "speedup_vs_dense": {"rebuild": dense_best / ms_step, "reuse": dense_best / reuse_ms,
