@@ -375,11 +375,12 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       for (int i = tid; i < ST_B * 128; i += ST_THREADS) sHist[i] = 0;
       __syncthreads();
       {
-        // bucket = floor((hi - s) * inv): the subtraction first, so that s == hi gives exactly 0 and s > hi
-        // a negative bucket; rows that are not searching get hi = -inf and fall out the same way
+        // bucket = floor((hi - s) * inv): s > hi gives a negative bucket; rows that are not searching get
+        // hi = -inf and fall out the same way
         const bool act = sRowI[R_STATE * 128 + r] == RS_SEARCH;
         const float hi = act ? sRowF[R_HI * 128 + r] : -INFINITY;
         const float inv = act ? sRowF[R_INV * 128 + r] : 1.0f;
+        const float ninv = -inv, hiinv = hi * inv;
         // with an overflow bucket, bucket 0 takes every score above hi and the range starts at bucket 1
         const int ovf = act ? sRowI[R_OVF * 128 + r] : 0;
         const int bmin = ovf - 1;
@@ -392,8 +393,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
               // floor by an add rounded toward -inf: 1.5 * 2^23 + t has floor(t) in its low mantissa bits for
-              // |t| < 2^22; beyond that the difference keeps the sign of t and is far outside [0, ST_B)
-              const float t = (hi - __uint_as_float(v[j4 + e])) * inv;
+              // |t| < 2^22; beyond that the difference keeps the sign of t and is far outside [0, ST_B).
+              // t = (hi - s) inv as one multiply-add: a score within a rounding step of a bucket boundary may
+              // land in the neighbouring bucket, which only moves the window (the selection is validated
+              // against exact keys afterwards)
+              const float t = __fmaf_rd(__uint_as_float(v[j4 + e]), ninv, hiinv);
               const int b = max(__float_as_int(__fadd_rd(t, 12582912.0f)) - 0x4B400000 + ovf, bmin);
               if ((unsigned)b < (unsigned)ST_B) atomicAdd(hist_r + b * 128, pp[e]);
             }
@@ -494,17 +498,15 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
         uint32_t wbits = 0u, ibits = 0u;
 #pragma unroll
         for (int j4 = 0; j4 < 32; j4 += 4) {
-          const int4 p4 = *reinterpret_cast<const int4*>(sSizeP + cbase + j4);
-          const int pp[4] = {p4.x, p4.y, p4.z, p4.w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             const float a = __uint_as_float(v[j4 + e]);
-            const bool above = a > thrA;
-            sumA += above ? pp[e] : 0;
-            wbits |= above ? (1u << (j4 + e)) : 0u;
+            wbits |= a > thrA ? (1u << (j4 + e)) : 0u;
             ibits |= a >= thrW ? (1u << (j4 + e)) : 0u;
           }
         }
+        // sizes of the (few) clusters above the window
+        for (uint32_t wb = wbits; wb; wb &= wb - 1u) sumA += sSizeP[cbase + __ffs(wb) - 1];
         uint32_t cbits = ibits & ~wbits;
         while (cbits) {
           const int j = __ffs(cbits) - 1;
