@@ -495,16 +495,18 @@ __global__ void __launch_bounds__(ST_THREADS, 1) select_tc_kernel(
       stream([&](int cbase, const uint32_t(&v)[32]) {
         // straight-line over the 32 scores: bit masks of the clusters above the window and of those at or
         // above its lower end; the (few) candidates are appended afterwards from the difference
-        uint32_t wbits = 0u, ibits = 0u;
+        // The comparisons as sign bits of differences (a > thrA iff thrA - a < 0; a >= thrW iff not a - thrW < 0),
+        // shifted into the masks from score 31 down to score 0: a subtraction on the FMA pipe and a funnel shift
+        // per bit instead of a compare and a predicated OR on the half-rate ALU pipe.  (Rows that do not collect
+        // have thrA = thrW = +inf: no bit of either mask.)
+        uint32_t wbits = 0u, nbits = 0u;
 #pragma unroll
-        for (int j4 = 0; j4 < 32; j4 += 4) {
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const float a = __uint_as_float(v[j4 + e]);
-            wbits |= a > thrA ? (1u << (j4 + e)) : 0u;
-            ibits |= a >= thrW ? (1u << (j4 + e)) : 0u;
-          }
+        for (int j = 31; j >= 0; --j) {
+          const float a = __uint_as_float(v[j]);
+          wbits = __funnelshift_l(__float_as_uint(thrA - a), wbits, 1);
+          nbits = __funnelshift_l(__float_as_uint(a - thrW), nbits, 1);
         }
+        const uint32_t ibits = ~nbits;
         // sizes of the (few) clusters above the window
         for (uint32_t wb = wbits; wb; wb &= wb - 1u) sumA += sSizeP[cbase + __ffs(wb) - 1];
         uint32_t cbits = ibits & ~wbits;
