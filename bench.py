@@ -533,7 +533,7 @@ def run_ours(args, rank, world, local_rank):
                                 "frac_of_tensor_peak": 2 * 32 * scores / t_sel / 1e12 / pk["tf"],
                                 "algorithmic_GBps": sel_bytes / t_sel / 1e9,
                                 "frac_of_hbm_peak": sel_bytes / t_sel / 1e9 / pk["hbm"],
-                                "bound": "integer / compare instruction issue (about 27 instructions per score)"}
+                                "bound": "integer / compare instruction issue (about 22 instructions per score over the two passes)"}
     tail_flops = float(N) * 2048 * (2 * 32 + 2 * W["D"]) * Hl
     if stages.get("residual_merge"):
         stage_roof["residual_merge"] = {"ms": stages["residual_merge"],
