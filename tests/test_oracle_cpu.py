@@ -160,6 +160,36 @@ def test_empty_union_is_the_pure_centroid_residual():
     assert torch.allclose(out[0], want, atol=1e-4, rtol=1e-4)
 
 
+@pytest.mark.parametrize("tailw", [1.0, 0.5])
+def test_partial_union_is_one_softmax_over_union_keys_and_unselected_centroids(tailw):
+    """The two-stage form (exact part with its log-sum-exp, then the merge with the centroid residual) against
+    the single formula it implements, evaluated query by query in float64: every key of the query cluster's
+    union enters with its true logit and its value, every key cluster outside the union enters once with the
+    fp16-rounded centroid logit, weight n_c in the denominator and lam * sumv_c in the numerator, both scaled
+    by tailw (tile_attn/src/kernel.cu:1248-1449)."""
+    p = _tiny_problem(N=256, seed=11)
+    scale = 1.0 / math.sqrt(128.0)
+    g = torch.Generator().manual_seed(5)
+    sel = torch.rand(1, p["CQ"], 2048, generator=g) < 0.3        # a third of the key clusters per query cluster
+    unip = O.pack_bits(sel)
+    o, lse = O.exact_attention(p["q"], p["k"], p["v"], p["qlab"], p["klab"], unip, scale)
+    got = O.residual_merge(o, lse, p["QU"], p["cks"], p["sumv"], p["lam"], p["kcounts"], unip, p["qlab"], tailw)
+    gl = O.chain_dot(p["QU"][0].float(), p["cks"][0].float()).half().double()      # [N, C] centroid logits
+    q, k, v = (p[n][0].double() for n in ("q", "k", "v"))
+    klab, qlab = p["klab"][0].long(), p["qlab"][0].long()
+    nc, sumv, lam = p["kcounts"][0].double(), p["sumv"][0].double(), float(p["lam"][0])
+    for i in range(0, 256, 7):
+        inside = sel[0, qlab[i]]                                  # [C] clusters of this query's union
+        keys = inside[klab].nonzero()[:, 0]
+        s = (k[keys] @ q[i]) * scale
+        gi = gl[i][~inside]
+        m = max(float(s.max()) if keys.numel() else -math.inf, float(gi.max()))
+        es, eg = torch.exp(s - m), torch.exp(gi - m)
+        num = es @ v[keys] + tailw * lam * (eg @ sumv[~inside])
+        den = es.sum() + tailw * (eg * nc[~inside]).sum()
+        assert torch.allclose(got[0, i].double(), num / den, atol=2e-5, rtol=1e-4), i
+
+
 def test_reuse_schedule_follows_the_reference_rule():
     """Rebuild iff no snapshot, the step counter went backwards, or branch 0 with
     step - snapshot_step >= mask_refresh (deploy_step.py:297-309)."""
