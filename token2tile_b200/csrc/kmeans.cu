@@ -9,6 +9,8 @@
 // reproducible bit for bit: distances are fp32 fused-multiply-add chains in a
 // fixed order, sums are either integers or accumulated in grouped row order by
 // one owner warp.
+#include <mutex>
+
 #include "common.cuh"
 #include "internal.h"
 
@@ -449,6 +451,7 @@ struct Carver {
 
 struct KmmWs {
   int *qlab1, *chist, *cbase_q, *cbase_k, *amb;
+  int *chist_k, *amb_k;      // the key side runs next to the query side and needs scratch of its own
   __nv_bfloat16* cq1;
   float *vsum, *bmax;
   size_t total;
@@ -459,7 +462,9 @@ static KmmWs kmm_layout(int H, int N, int CQ, int C, void* base) {
   const int nChunk = cdiv(N, GR_CHUNK);
   w.qlab1 = cv.take<int>((size_t)H * N);
   w.amb = cv.take<int>((size_t)H * N + 1);
-  w.chist = cv.take<int>((size_t)H * nChunk * (C > CQ ? C : CQ));
+  w.chist = cv.take<int>((size_t)H * nChunk * CQ);
+  w.amb_k = cv.take<int>((size_t)H * N + 1);
+  w.chist_k = cv.take<int>((size_t)H * nChunk * C);
   w.cbase_q = cv.take<int>((size_t)H * CQ);
   w.cbase_k = cv.take<int>((size_t)H * C);
   w.cq1 = cv.take<__nv_bfloat16>((size_t)H * CQ * kR);
@@ -503,6 +508,33 @@ static bool group_smem_ok(int Cn) {
 }
 
 static int finish() { return cudaGetLastError() == cudaSuccess ? T2T_OK : T2T_ERR_CUDA; }
+
+// A stream of the library's own per device, for work that is independent of what the caller's stream is doing
+// inside one call: forked from the caller's stream by an event and joined back by another before the call
+// returns, so the caller sees one ordered call.  The mutex is held while a call issues its work: two host
+// threads must not interleave their records of the shared events.
+struct SideStream {
+  bool ready;
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+  std::mutex issue;
+};
+static SideStream* side_stream() {
+  static SideStream table[64];
+  static std::mutex create;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(create);
+  SideStream* s = &table[dev];
+  if (!s->ready) {
+    if (cudaStreamCreateWithFlags(&s->stream, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s->fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&s->join, cudaEventDisableTiming) != cudaSuccess)
+      return nullptr;
+    s->ready = true;
+  }
+  return s;
+}
 
 }  // namespace t2t
 
@@ -563,28 +595,44 @@ extern "C" int t2t_kmeans_maintain_strided(const void* QU, const void* KU, const
   if (ws_bytes < w.total) return T2T_ERR_WORKSPACE;
   int rc;
   const dim3 qgrid(cdiv(CQ, CS_WARPS), H), kgrid(cdiv(C, CS_WARPS), H);
+  // The key side (assignment, grouping, means, value statistics) does not depend on the query side: it runs on
+  // the library's side stream, next to the two query passes on the caller's.
+  SideStream* side = side_stream();
+  if (!side) return T2T_ERR_CUDA;
+  std::lock_guard<std::mutex> issuing(side->issue);
+  const cudaStream_t sk = side->stream;
+  if (cudaEventRecord(side->fork, st) != cudaSuccess || cudaStreamWaitEvent(sk, side->fork, 0) != cudaSuccess)
+    return T2T_ERR_CUDA;
+  rc = launch_assign((const bf16*)KU, (const bf16*)ck0, (int*)klab, H, N, C, pin_tail > 0 ? N - pin_tail : -1,
+                     C - 1, w.amb_k, d_status, sk);
+  if (rc == T2T_OK) {
+    launch_group((const int*)klab, w.chist_k, (int*)kcounts, w.cbase_k, (int*)kperm, H, N, C, sk);
+    key_mean_kernel<<<kgrid, CS_WARPS * 32, 0, sk>>>((const bf16*)KU, (const int*)kperm, (const int*)kcounts,
+                                                    w.cbase_k, (const bf16*)ck0, (float*)ck2, (bf16*)ck16,
+                                                    (bf16*)cks16, scale, N, C);
+    launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase_k, (bf16*)V_sorted, (bf16*)sumv,
+                  (float*)lam, w.vsum, w.bmax, H, N, C, v_row_stride, v_head_stride, sk);
+  }
+  const bool recorded = cudaEventRecord(side->join, sk) == cudaSuccess;
+  // whatever happens below, the caller's stream ends up ordered behind the side stream again
+  auto join = [&]() { return recorded && cudaStreamWaitEvent(st, side->join, 0) == cudaSuccess; };
+  if (rc != T2T_OK || !recorded) {
+    join();
+    return rc != T2T_OK ? rc : T2T_ERR_CUDA;
+  }
   // queries, pass 1
   rc = launch_assign((const bf16*)QU, (const bf16*)cq0, w.qlab1, H, N, CQ, -1, 0, w.amb, d_status, st);
-  if (rc != T2T_OK) return rc;
+  if (rc != T2T_OK) { join(); return rc; }
   launch_group(w.qlab1, w.chist, (int*)qcounts, w.cbase_q, (int*)qperm, H, N, CQ, st);
   fixed_mean_kernel<<<qgrid, CS_WARPS * 32, 0, st>>>((const bf16*)QU, (const int*)qperm, (const int*)qcounts,
                                                     w.cbase_q, (const bf16*)cq0, w.cq1, N, CQ);
   // queries, pass 2
   rc = launch_assign((const bf16*)QU, w.cq1, (int*)qlab, H, N, CQ, -1, 0, w.amb, d_status, st);
-  if (rc != T2T_OK) return rc;
+  if (rc != T2T_OK) { join(); return rc; }
   launch_group((const int*)qlab, w.chist, (int*)qcounts, w.cbase_q, (int*)qperm, H, N, CQ, st);
   fixed_mean_kernel<<<qgrid, CS_WARPS * 32, 0, st>>>((const bf16*)QU, (const int*)qperm, (const int*)qcounts,
                                                     w.cbase_q, w.cq1, (bf16*)cq2, N, CQ);
-  // keys
-  rc = launch_assign((const bf16*)KU, (const bf16*)ck0, (int*)klab, H, N, C, pin_tail > 0 ? N - pin_tail : -1,
-                     C - 1, w.amb, d_status, st);
-  if (rc != T2T_OK) return rc;
-  launch_group((const int*)klab, w.chist, (int*)kcounts, w.cbase_k, (int*)kperm, H, N, C, st);
-  key_mean_kernel<<<kgrid, CS_WARPS * 32, 0, st>>>((const bf16*)KU, (const int*)kperm, (const int*)kcounts,
-                                                  w.cbase_k, (const bf16*)ck0, (float*)ck2, (bf16*)ck16,
-                                                  (bf16*)cks16, scale, N, C);
-  launch_vstats((const bf16*)V, (const int*)kperm, (const int*)kcounts, w.cbase_k, (bf16*)V_sorted, (bf16*)sumv,
-                (float*)lam, w.vsum, w.bmax, H, N, C, v_row_stride, v_head_stride, st);
+  if (!join()) return T2T_ERR_CUDA;
   return finish();
 }
 
