@@ -95,7 +95,9 @@ int t2t_centroid_update(const void* x, const void* labels, const void* old, void
  * divided by lam), lam fp32 [H].  The last pin_tail keys are forced into
  * cluster C-1.  Replaces kmeans_maintain_launch,
  * kernels/kmeans_maintain/src/kernels.h:5-13 (kernels.cu:787-876) and the casts
- * at deploy_step.py:389-393. */
+ * at deploy_step.py:389-393.  The key side runs on a stream the library creates
+ * once per device, forked from `stream` by an event and joined back before the
+ * call returns: the caller sees one call ordered on its stream. */
 size_t t2t_kmeans_maintain_ws_bytes(int H, int N, int CQ, int C);
 int t2t_kmeans_maintain(const void* QU, const void* KU, const void* V, const void* cq0, const void* ck0,
                         void* qlab, void* cq2, void* klab, void* ck2, void* ck16, void* cks16,
